@@ -38,6 +38,8 @@ class CacheView:
                                             # ids: int32 [pages, PAGE]
     block_table: Optional[torch.Tensor] = None   # kv: int32 [max_seqs, max_pages_per_seq]
     state: Optional[torch.Tensor] = None    # state: [max_seqs, *state_shape]
+    state_offset: int = 0                   # floats of a state copy that lie before the reader's own (a block that keeps
+                                            # something of its own in the same state block puts its mixer behind it)
     window: Optional[int] = None
     keep_first: int = 0
 

@@ -1,0 +1,347 @@
+// Attention over a cached latent: every position keeps one normed latent vector c [R] and one rotated key part k_rot [dr]
+// shared by all heads, nothing per head.  A head's key is [W_uk,h c | k_rot] and its value W_uv,h c; because both are linear
+// in c, the up-projections are moved off the keys: with q' = W_uk,h^T q_nope the score is (q' . c + q_rot . k_rot) * scale, and
+// the output is W_uv,h (sum_j p_j c_j).  So the kernel below is attention of H query heads on ONE key of R + dr lanes per
+// position whose first R lanes are also the value; the two small products per head (q' before, W_uv after) are batched
+// matrix products outside it.
+//
+//   blm_latent_prepare    q projection -> q_nope [H][N][dk] (the batched product's operand) and rotated q_rot [N][H][dr];
+//                         down projection -> RMS-normed c and rotated k_rot, appended to the token's place in the cache
+//   blm_latent_attention  causal softmax attention of a step's rows over the cache, keys cut over `splits` blocks
+//   blm_sigmoid_gate      out = o * sigmoid(g)
+//
+// Cache page: [page_size][R + dr] in the cache's dtype.  Scores, softmax and sums are fp32 in both dtypes.
+#include "common.cuh"
+
+BLM_API const char* blm_attention_latent_last_error() { return g_blm_error; }
+
+// lanes 2i and 2i + 1 of a rotated part turn by pos * freq[i]; lanes from rot_dims on pass unchanged.  The angle, its sine
+// and cosine are taken in fp64 and applied in fp32.
+__device__ __forceinline__ float rotated_lane(const float* src, int j, int rot_dims, int pos, const double* __restrict__ freq) {
+    if (j >= rot_dims) return src[j];
+    const int i = j >> 1;
+    double s, c;
+    sincos((double)pos * freq[i], &s, &c);
+    const float a = src[2 * i], b = src[2 * i + 1], cf = (float)c, sf = (float)s;
+    return (j & 1) ? b * cf + a * sf : a * cf - b * sf;
+}
+
+template <typename T>
+__global__ void latent_prepare_kernel(const float* __restrict__ qp, long long qp_stride, const float* __restrict__ dkv,
+                                      long long dkv_stride, const float* __restrict__ c_weight, float eps,
+                                      const double* __restrict__ freq, int rot_dims, T* __restrict__ q_nope,
+                                      float* __restrict__ q_rot, T* __restrict__ pool, const int* __restrict__ token_seq,
+                                      const int* __restrict__ token_pos, const int* __restrict__ slot_of_seq,
+                                      const int* __restrict__ block_table, int table_stride, int n_tokens, int H, int dk, int dr,
+                                      int R, int page_size) {
+    __shared__ float red[33];
+    const int n = blockIdx.x;
+    const int seq = token_seq[n];
+    const bool real = seq >= 0;                 // a row of no sequence leaves zeros and reaches no cache
+    const int pos = real ? token_pos[n] : 0;
+    const float* qrow = qp + (size_t)n * qp_stride;
+    for (int idx = threadIdx.x; idx < H * dk; idx += blockDim.x) {
+        const int h = idx / dk, d = idx % dk;
+        q_nope[((size_t)h * n_tokens + n) * dk + d] = from_f32<T>(real ? qrow[(size_t)h * (dk + dr) + d] : 0.f);
+    }
+    for (int idx = threadIdx.x; idx < H * dr; idx += blockDim.x) {
+        const int h = idx / dr, j = idx % dr;
+        q_rot[((size_t)n * H + h) * dr + j] = real ? rotated_lane(qrow + (size_t)h * (dk + dr) + dk, j, rot_dims, pos, freq) : 0.f;
+    }
+    if (!real) return;
+    const float* row = dkv + (size_t)n * dkv_stride;
+    float ss = 0.f;
+    for (int r = threadIdx.x; r < R; r += blockDim.x) ss += row[r] * row[r];
+    const float total = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(total / (float)R + eps);
+    const int page = block_table[(size_t)slot_of_seq[seq] * table_stride + pos / page_size];
+    T* dst = pool + ((size_t)page * page_size + pos % page_size) * (R + dr);
+    for (int r = threadIdx.x; r < R; r += blockDim.x) dst[r] = from_f32<T>(row[r] * inv * c_weight[r]);
+    for (int j = threadIdx.x; j < dr; j += blockDim.x) dst[R + j] = from_f32<T>(rotated_lane(row + R, j, rot_dims, pos, freq));
+}
+
+BLM_API int blm_latent_prepare(const float* qp, long long qp_stride, const float* dkv, long long dkv_stride, const float* c_weight,
+                               float eps, const double* freq, int rot_dims, void* q_nope, float* q_rot, void* pool, int dtype,
+                               const int* token_seq, const int* token_pos, const int* slot_of_seq, const int* block_table,
+                               int table_stride, int n_tokens, int H, int dk, int dr, int R, int page_size, cudaStream_t stream) {
+    if (n_tokens == 0) return BLM_OK;
+    BLM_REQUIRE(H > 0 && dk > 0 && dr >= 0 && R > 0 && page_size > 0, "latent_prepare: bad sizes");
+    BLM_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= dr, "latent_prepare: %d rotated lanes of %d", rot_dims, dr);
+    if (dtype == BLM_F32)
+        latent_prepare_kernel<float><<<n_tokens, 256, 0, stream>>>(qp, qp_stride, dkv, dkv_stride, c_weight, eps, freq, rot_dims,
+                                                                   (float*)q_nope, q_rot, (float*)pool, token_seq, token_pos,
+                                                                   slot_of_seq, block_table, table_stride, n_tokens, H, dk, dr, R,
+                                                                   page_size);
+    else if (dtype == BLM_BF16)
+        latent_prepare_kernel<__nv_bfloat16><<<n_tokens, 256, 0, stream>>>(qp, qp_stride, dkv, dkv_stride, c_weight, eps, freq, rot_dims,
+                                                                           (__nv_bfloat16*)q_nope, q_rot, (__nv_bfloat16*)pool,
+                                                                           token_seq, token_pos, slot_of_seq, block_table,
+                                                                           table_stride, n_tokens, H, dk, dr, R, page_size);
+    else
+        return blm_fail(BLM_BAD_ARGUMENT, "latent_prepare: dtype %d", dtype);
+    return blm_check_launch("latent_prepare");
+}
+
+// ---------------------------------------------------------------------------------------------
+// attention.  A block owns kTM rows of one sequence (row = new token x head, the heads of a token side by side: they
+// all read the same keys) and one share of the keys; keys pass through shared memory kKC at a time, in fp32.  Thread t
+// holds the output columns t, t + 256, ... of all kTM rows.
+// ---------------------------------------------------------------------------------------------
+constexpr int kTM = 16, kKC = 32, kLatThreads = 256;
+
+template <typename T, typename TO, int CPT>
+__global__ void __launch_bounds__(kLatThreads)
+    latent_attention_kernel(const float* __restrict__ q_lat, const float* __restrict__ q_rot, const T* __restrict__ pool,
+                            const int* __restrict__ block_table, int table_stride, const int* __restrict__ cu_seqlens,
+                            const int* __restrict__ slot_of_seq, const int* __restrict__ start_pos, TO* __restrict__ out,
+                            float* __restrict__ partial, int n_tokens, int H, int R, int dr, int page_size, float scale,
+                            int n_splits) {
+    const int seq = blockIdx.y, split = blockIdx.z;
+    const int first = cu_seqlens[seq];
+    const int n_new = cu_seqlens[seq + 1] - first;
+    if (n_new <= 0) return;
+    const int rows_total = n_new * H, r0 = blockIdx.x * kTM;
+    if (r0 >= rows_total) return;
+    const int n_rows = min(kTM, rows_total - r0);
+    const int start = start_pos[seq];
+    const int kv_end = start + (r0 + n_rows - 1) / H + 1;          // keys the tile's last row sees
+    const int pages_total = (kv_end + page_size - 1) / page_size;
+    const int pages_per = (pages_total + n_splits - 1) / n_splits;
+    const int key_lo = min(kv_end, split * pages_per * page_size), key_hi = min(kv_end, (split + 1) * pages_per * page_size);
+    const int D = R + dr, KS = D + 1;
+    extern __shared__ __align__(16) float lat_smem[];
+    float* Pt = lat_smem;                    // [kKC][kTM]: a chunk's weights, key by key
+    float* Qs = Pt + kKC * kTM;              // [kTM][D]
+    float* Ks = Qs + kTM * D;                // [kKC][D + 1]
+    float* Ss = Ks + kKC * KS;               // [kTM][kKC]
+    __shared__ float m_s[kTM], l_s[kTM], alpha_s[kTM];
+    __shared__ int page_of[kKC];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int* table = block_table + (size_t)slot_of_seq[seq] * table_stride;
+    for (int idx = tid; idx < kTM * D; idx += kLatThreads) {
+        const int row = idx / D, d = idx % D;
+        float v = 0.f;
+        if (row < n_rows) {
+            const int r = r0 + row, n = first + r / H, h = r % H;
+            v = d < R ? q_lat[((size_t)h * n_tokens + n) * R + d] : q_rot[((size_t)n * H + h) * dr + (d - R)];
+        }
+        Qs[idx] = v;
+    }
+    if (tid < kTM) {
+        m_s[tid] = -INFINITY;
+        l_s[tid] = 0.f;
+    }
+    float acc[kTM][CPT];
+#pragma unroll
+    for (int r = 0; r < kTM; ++r)
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) acc[r][c] = 0.f;
+    for (int k0 = key_lo; k0 < key_hi; k0 += kKC) {
+        const int nk = min(kKC, key_hi - k0);
+        __syncthreads();                     // the chunk before is used up (and Qs, m_s, l_s are written)
+        if (tid < kKC) page_of[tid] = tid < nk ? table[(k0 + tid) / page_size] : 0;
+        __syncthreads();
+        for (int idx = tid; idx < kKC * D; idx += kLatThreads) {
+            const int j = idx / D, d = idx % D;
+            float v = 0.f;
+            if (j < nk) v = to_f32(pool[((size_t)page_of[j] * page_size + (k0 + j) % page_size) * D + d]);
+            Ks[j * KS + d] = v;
+        }
+        __syncthreads();
+        {                                    // scores: thread (row, key pair)
+            const int row = tid >> 4, jp = tid & 15;
+            const float* qr = Qs + row * D;
+            const float* ka = Ks + jp * KS;
+            const float* kb = Ks + (jp + 16) * KS;
+            float sa = 0.f, sb = 0.f;
+            for (int d = 0; d < D; ++d) {
+                const float qv = qr[d];
+                sa = fmaf(qv, ka[d], sa);
+                sb = fmaf(qv, kb[d], sb);
+            }
+            const int limit = start + (r0 + row) / H;            // the row's own position
+            const bool live = row < n_rows;
+            Ss[row * kKC + jp] = (live && jp < nk && k0 + jp <= limit) ? sa * scale : -INFINITY;
+            Ss[row * kKC + jp + 16] = (live && jp + 16 < nk && k0 + jp + 16 <= limit) ? sb * scale : -INFINITY;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {     // running softmax: a warp takes two rows, a lane a key
+            const int row = 2 * warp + rr;
+            const float s = Ss[row * kKC + lane];
+            const float m_old = m_s[row];
+            const float m_new = fmaxf(m_old, warp_max(s));
+            float p = 0.f, alpha = 1.f;
+            if (m_new > -INFINITY) {
+                p = s > -INFINITY ? expf(s - m_new) : 0.f;
+                alpha = m_old > -INFINITY ? expf(m_old - m_new) : 0.f;
+            }
+            const float sum = warp_sum(p);
+            Pt[lane * kTM + row] = p;
+            if (lane == 0) {
+                m_s[row] = m_new;
+                l_s[row] = l_s[row] * alpha + sum;
+                alpha_s[row] = alpha;
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < kTM; ++r) {
+            const float a = alpha_s[r];
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) acc[r][c] *= a;
+        }
+        for (int j = 0; j < nk; ++j) {
+            float p[kTM];
+#pragma unroll
+            for (int r4 = 0; r4 < kTM / 4; ++r4) {
+                const float4 v = *reinterpret_cast<const float4*>(Pt + j * kTM + 4 * r4);
+                p[4 * r4] = v.x; p[4 * r4 + 1] = v.y; p[4 * r4 + 2] = v.z; p[4 * r4 + 3] = v.w;
+            }
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) {
+                const int col = tid + c * kLatThreads;
+                const float v = col < R ? Ks[j * KS + col] : 0.f;
+#pragma unroll
+                for (int r = 0; r < kTM; ++r) acc[r][c] = fmaf(p[r], v, acc[r][c]);
+            }
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < kTM; ++r) {
+        if (r >= n_rows) break;
+        const int rr = r0 + r, n = first + rr / H, h = rr % H;
+        if (n_splits == 1) {
+            const float inv = 1.0f / l_s[r];
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) {
+                const int col = tid + c * kLatThreads;
+                if (col < R) out[((size_t)h * n_tokens + n) * R + col] = from_f32<TO>(acc[r][c] * inv);
+            }
+        } else {
+            float* dst = partial + ((size_t)split * n_tokens * H + (size_t)n * H + h) * (R + 2);
+            if (tid == 0) {
+                dst[0] = m_s[r];
+                dst[1] = l_s[r];
+            }
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) {
+                const int col = tid + c * kLatThreads;
+                if (col < R) dst[2 + col] = acc[r][c];
+            }
+        }
+    }
+}
+
+// the shares of a row's keys, merged in the order of the shares
+template <typename TO>
+__global__ void latent_combine_kernel(const float* __restrict__ partial, const int* __restrict__ token_seq, TO* __restrict__ out,
+                                      int n_tokens, int H, int R, int n_splits) {
+    const int n = blockIdx.x / H, h = blockIdx.x % H;
+    if (token_seq[n] < 0) return;            // a row of no sequence: nothing was written for it, the caller's zeros stay
+    const size_t stride = (size_t)n_tokens * H * (R + 2);
+    const float* src = partial + ((size_t)n * H + h) * (R + 2);
+    float m = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) m = fmaxf(m, src[s * stride]);
+    float l = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+        const float ms = src[s * stride];
+        if (ms > -INFINITY) l += src[s * stride + 1] * expf(ms - m);
+    }
+    const float inv = 1.0f / l;
+    for (int c = threadIdx.x; c < R; c += blockDim.x) {
+        float o = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float ms = src[s * stride];
+            if (ms > -INFINITY) o += src[s * stride + 2 + c] * expf(ms - m);
+        }
+        out[((size_t)h * n_tokens + n) * R + c] = from_f32<TO>(o * inv);
+    }
+}
+
+BLM_API long long blm_latent_attention_scratch_floats(int n_tokens, int H, int R, int n_splits) {
+    return n_splits > 1 ? (long long)n_splits * n_tokens * H * (R + 2) : 0;
+}
+
+// q_lat float32 [H][N][R], q_rot float32 [N][H][dr]; out [H][N][R] in `out_dtype` (rows of no sequence are left alone);
+// partial: float32 scratch of blm_latent_attention_scratch_floats when n_splits > 1.
+BLM_API int blm_latent_attention(const float* q_lat, const float* q_rot, const void* pool, int dtype, const int* block_table,
+                                 int table_stride, const int* cu_seqlens, const int* slot_of_seq, const int* start_pos,
+                                 const int* token_seq, void* out, int out_dtype, float* partial, int n_tokens, int n_seqs,
+                                 int max_q_len, int H, int R, int dr, int page_size, float scale, int n_splits,
+                                 cudaStream_t stream) {
+    if (n_tokens == 0 || n_seqs == 0) return BLM_OK;
+    BLM_REQUIRE(H > 0 && R > 0 && dr >= 0 && page_size > 0 && max_q_len > 0 && n_splits >= 1, "latent_attention: bad sizes");
+    BLM_REQUIRE(R <= 4 * kLatThreads, "latent_attention: a latent of %d lanes; this kernel takes up to %d", R, 4 * kLatThreads);
+    BLM_REQUIRE(n_splits == 1 || partial != nullptr, "latent_attention: key shares need their scratch");
+    const int D = R + dr;
+    const size_t smem = ((size_t)kKC * kTM + (size_t)kTM * D + (size_t)kKC * (D + 1) + (size_t)kTM * kKC) * sizeof(float);
+    BLM_REQUIRE(smem <= 200 * 1024, "latent_attention: keys of %d lanes need %zu bytes of shared memory", D, smem);
+    const long long tiles = ((long long)max_q_len * H + kTM - 1) / kTM;
+    BLM_REQUIRE(tiles < (1ll << 31) && n_seqs <= 65535 && n_splits <= 65535, "latent_attention: too many blocks");
+    const dim3 grid((unsigned)tiles, (unsigned)n_seqs, (unsigned)n_splits);
+    const int cpt = (R + kLatThreads - 1) / kLatThreads;
+#define BLM_LAT(T, TO, CPT)                                                                                              \
+    {                                                                                                                    \
+        auto kern = latent_attention_kernel<T, TO, CPT>;                                                                 \
+        if (smem > 48 * 1024) {                                                                                          \
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);          \
+            if (e != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "latent_attention: %s", cudaGetErrorString(e));        \
+        }                                                                                                                \
+        kern<<<grid, kLatThreads, smem, stream>>>(q_lat, q_rot, (const T*)pool, block_table, table_stride, cu_seqlens,   \
+                                                  slot_of_seq, start_pos, (TO*)out, partial, n_tokens, H, R, dr,         \
+                                                  page_size, scale, n_splits);                                           \
+    }
+#define BLM_LAT_C(T, TO)                                                 \
+    if (cpt == 1) BLM_LAT(T, TO, 1)                                      \
+    else if (cpt == 2) BLM_LAT(T, TO, 2)                                 \
+    else if (cpt == 3) BLM_LAT(T, TO, 3)                                 \
+    else BLM_LAT(T, TO, 4)
+    if (dtype == BLM_F32 && out_dtype == BLM_F32) { BLM_LAT_C(float, float) }
+    else if (dtype == BLM_BF16 && out_dtype == BLM_BF16) { BLM_LAT_C(__nv_bfloat16, __nv_bfloat16) }
+    else if (dtype == BLM_BF16 && out_dtype == BLM_F32) { BLM_LAT_C(__nv_bfloat16, float) }
+    else return blm_fail(BLM_BAD_ARGUMENT, "latent_attention: dtypes %d/%d", dtype, out_dtype);
+#undef BLM_LAT_C
+#undef BLM_LAT
+    int rc = blm_check_launch("latent_attention");
+    if (rc != BLM_OK || n_splits == 1) return rc;
+    if (out_dtype == BLM_F32)
+        latent_combine_kernel<float><<<n_tokens * H, 128, 0, stream>>>(partial, token_seq, (float*)out, n_tokens, H, R, n_splits);
+    else
+        latent_combine_kernel<__nv_bfloat16><<<n_tokens * H, 128, 0, stream>>>(partial, token_seq, (__nv_bfloat16*)out, n_tokens, H, R,
+                                                                              n_splits);
+    return blm_check_launch("latent_attention (combine)");
+}
+
+// ---------------------------------------------------------------------------------------------
+// out = o * sigmoid(g), element by element: o, out [N][C]; g [N][g_stride] in float32 or the activations' dtype
+// ---------------------------------------------------------------------------------------------
+template <typename T, typename TG>
+__global__ void sigmoid_gate_kernel(const T* __restrict__ o, const TG* __restrict__ g, long long g_stride, T* __restrict__ out,
+                                    int cols) {
+    const int n = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= cols) return;
+    const size_t i = (size_t)n * cols + c;
+    out[i] = from_f32<T>(to_f32(o[i]) / (1.0f + expf(-to_f32(g[(size_t)n * g_stride + c]))));
+}
+
+BLM_API int blm_sigmoid_gate(const void* o, int dtype, const void* g, int g_dtype, long long g_stride, void* out, int rows, int cols,
+                             cudaStream_t stream) {
+    if (rows == 0 || cols == 0) return BLM_OK;
+    BLM_REQUIRE(rows > 0 && rows <= 65535 && cols > 0, "sigmoid_gate: bad sizes");
+    const int threads = 256;
+    const dim3 grid((cols + threads - 1) / threads, rows);
+    if (dtype == BLM_F32 && g_dtype == BLM_F32)
+        sigmoid_gate_kernel<float, float><<<grid, threads, 0, stream>>>((const float*)o, (const float*)g, g_stride, (float*)out, cols);
+    else if (dtype == BLM_BF16 && g_dtype == BLM_F32)
+        sigmoid_gate_kernel<__nv_bfloat16, float><<<grid, threads, 0, stream>>>((const __nv_bfloat16*)o, (const float*)g, g_stride,
+                                                                                (__nv_bfloat16*)out, cols);
+    else if (dtype == BLM_BF16 && g_dtype == BLM_BF16)
+        sigmoid_gate_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, threads, 0, stream>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)g,
+                                                                                        g_stride, (__nv_bfloat16*)out, cols);
+    else
+        return blm_fail(BLM_BAD_ARGUMENT, "sigmoid_gate: dtypes %d/%d", dtype, g_dtype);
+    return blm_check_launch("sigmoid_gate");
+}

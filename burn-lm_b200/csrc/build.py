@@ -37,6 +37,7 @@ MODULES = {
     "stream_ops": ["stream_ops.cu"],
     "recurrent": ["recurrent.cu"],
     "attention_sigmoid": ["attention_sigmoid.cu"],
+    "attention_latent": ["attention_latent.cu"],
     "gemm": ["gemm_f32.cu"],
     "gemv": ["gemv.cu"],
     "gemm_tc": ["gemm_tc.cu"],

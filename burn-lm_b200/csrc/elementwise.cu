@@ -63,15 +63,15 @@ BLM_API int blm_embed(const int* tokens, const void* table, int table_dtype, flo
 //   rows != nullptr: out[i] = norm(resid[rows[i]] + delta[rows[i]]), resid is left as it is
 // delta may be null (nothing to add).  gamma is fp32 or bf16 whatever the activations are.
 // ---------------------------------------------------------------------------------------------
-template <typename TA, typename TG>
-__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TA* __restrict__ delta,
+template <typename TA, typename TG, typename TD>
+__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
                                    const TG* __restrict__ gamma, TA* __restrict__ out,
                                    const int* __restrict__ rows, int width, float eps) {
     extern __shared__ float row_buf[];  // [width] + 33 for the reduction
     float* red = row_buf + width;
     const int src = rows ? rows[blockIdx.x] : blockIdx.x;
     float* r = resid + (size_t)src * width;
-    const TA* dl = delta ? delta + (size_t)src * width : nullptr;
+    const TD* dl = delta ? delta + (size_t)src * width : nullptr;
     float ss = 0.f;
     for (int d = threadIdx.x; d < width; d += blockDim.x) {
         float h = r[d];
@@ -140,10 +140,10 @@ __global__ void add_rmsnorm_bf16_vec_kernel(float* __restrict__ resid, const __n
     }
 }
 
-template <typename TA, typename TG>
+template <typename TA, typename TG, typename TD = TA>
 static int launch_add_rmsnorm(float* resid, const void* delta, const void* gamma, void* out,
                               const int* rows, int n_rows, int width, float eps, cudaStream_t stream) {
-    if (sizeof(TA) == 2 && width % 8 == 0 && width <= 256 * 8 * 4 && ((size_t)resid & 15) == 0 && ((size_t)out & 15) == 0 &&
+    if (sizeof(TA) == 2 && sizeof(TD) == 2 && width % 8 == 0 && width <= 256 * 8 * 4 && ((size_t)resid & 15) == 0 && ((size_t)out & 15) == 0 &&
         (delta == nullptr || ((size_t)delta & 15) == 0)) {
         const int threads = width >= 2048 ? 256 : 128;
         if (width <= threads * 8 * 4) {
@@ -154,21 +154,28 @@ static int launch_add_rmsnorm(float* resid, const void* delta, const void* gamma
     }
     const size_t smem = (size_t)(width + 33) * sizeof(float);
     BLM_REQUIRE(smem <= 200 * 1024, "rms norm: width %d is beyond the 51,000 this kernel holds in shared memory", width);
-    auto k = add_rmsnorm_kernel<TA, TG>;
+    auto k = add_rmsnorm_kernel<TA, TG, TD>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "rms norm: %s", cudaGetErrorString(e));
     }
     const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
-    k<<<n_rows, threads, smem, stream>>>(resid, (const TA*)delta, (const TG*)gamma, (TA*)out, rows, width, eps);
+    k<<<n_rows, threads, smem, stream>>>(resid, (const TD*)delta, (const TG*)gamma, (TA*)out, rows, width, eps);
     return blm_check_launch("add_rmsnorm");
 }
 
-BLM_API int blm_add_rmsnorm(float* resid, const void* delta, const void* gamma, int gamma_dtype,
+BLM_API int blm_add_rmsnorm(float* resid, const void* delta, int delta_dtype, const void* gamma, int gamma_dtype,
                             void* out, int act_dtype, const int* rows, int n_rows, int width,
                             float eps, cudaStream_t stream) {
     if (n_rows == 0) return BLM_OK;
     BLM_REQUIRE(n_rows > 0 && width > 0, "rms norm: bad sizes");
+    if (delta != nullptr && delta_dtype != act_dtype) {
+        // a float32 output of a sublayer added into the stream in front of a norm that hands bfloat16 on
+        BLM_REQUIRE(delta_dtype == BLM_F32 && act_dtype == BLM_BF16, "rms norm: delta dtype %d with out dtype %d", delta_dtype, act_dtype);
+        if (gamma_dtype == BLM_F32)
+            return launch_add_rmsnorm<__nv_bfloat16, float, float>(resid, delta, gamma, out, rows, n_rows, width, eps, stream);
+        return launch_add_rmsnorm<__nv_bfloat16, __nv_bfloat16, float>(resid, delta, gamma, out, rows, n_rows, width, eps, stream);
+    }
     if (act_dtype == BLM_F32 && gamma_dtype == BLM_F32)
         return launch_add_rmsnorm<float, float>(resid, delta, gamma, out, rows, n_rows, width, eps, stream);
     if (act_dtype == BLM_F32 && gamma_dtype == BLM_BF16)

@@ -10,7 +10,12 @@ constexpr int BM = 64, BN = 64, BK = 16;
 
 __global__ void __launch_bounds__(256) gemm_f32_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                                        float* __restrict__ y, int N, int M, int K,
-                                                       long long ldx, long long ldw, long long ldy) {
+                                                       long long ldx, long long ldw, long long ldy,
+                                                       long long bx, long long bw, long long by) {
+    // blockIdx.z: one product of a batch; bx, bw, by: the distance between two products' operands
+    x += (size_t)blockIdx.z * bx;
+    w += (size_t)blockIdx.z * bw;
+    y += (size_t)blockIdx.z * by;
     __shared__ float xs[BK][BM + 4];
     __shared__ float ws[BK][BN + 4];
     const int tid = threadIdx.x;
@@ -53,6 +58,17 @@ BLM_API int blm_gemm_f32(const float* x, const float* w, float* y, int N, int M,
     BLM_REQUIRE(N > 0 && M > 0 && K > 0, "gemm_f32: bad sizes %d %d %d", N, M, K);
     const dim3 grid((M + BN - 1) / BN, (N + BM - 1) / BM);
     BLM_REQUIRE(grid.y <= 65535, "gemm_f32: too many rows (%d)", N);
-    gemm_f32_kernel<<<grid, 256, 0, stream>>>(x, w, y, N, M, K, ldx, ldw, ldy);
+    gemm_f32_kernel<<<grid, 256, 0, stream>>>(x, w, y, N, M, K, ldx, ldw, ldy, 0, 0, 0);
     return blm_check_launch("gemm_f32");
+}
+
+// `batch` products y[b] = x[b] . W[b]^T of one shape in one launch; the operands of product b lie b * (bx, bw, by) elements on.
+BLM_API int blm_gemm_f32_batched(const float* x, const float* w, float* y, int batch, int N, int M, int K, long long ldx, long long ldw,
+                                 long long ldy, long long bx, long long bw, long long by, cudaStream_t stream) {
+    if (N == 0 || M == 0 || batch == 0) return BLM_OK;
+    BLM_REQUIRE(N > 0 && M > 0 && K > 0 && batch > 0 && batch <= 65535, "gemm_f32_batched: bad sizes %d x %d %d %d", batch, N, M, K);
+    const dim3 grid((M + BN - 1) / BN, (N + BM - 1) / BM, batch);
+    BLM_REQUIRE(grid.y <= 65535, "gemm_f32_batched: too many rows (%d)", N);
+    gemm_f32_kernel<<<grid, 256, 0, stream>>>(x, w, y, N, M, K, ldx, ldw, ldy, bx, bw, by);
+    return blm_check_launch("gemm_f32_batched");
 }

@@ -4,6 +4,10 @@
 //   z = W_router h (fp32), s = sigmoid(z); a token takes its `top` experts of largest s (ties: the lower index)
 //   with weight s (not renormalised).  weight_on_input: out = sum_k expert_k(s_k h); else out = sum_k s_k expert_k(h).
 //   expert(x) = W_down (silu(W_gate x) * (W_up x)).
+//   Options of the router: s = softmax(z) over all experts instead of the sigmoid; a correction [experts] added to the
+//   scores for the choice only (the weights are the scores without it); the chosen weights divided by their sum + 1e-20.
+//   Option of the experts: the clamped gated unit, g = min(W_gate x, limit), u = clamp(W_up x, -limit, limit),
+//   g * sigmoid(alpha g) * (u + 1).
 //
 // Everything runs on the device with sizes that depend on the step's token count only, so a step can be captured
 // in a CUDA graph: the grids cover the worst case (every expert's share padded to a tile) and blocks beyond the
@@ -17,10 +21,12 @@ BLM_API const char* blm_moe_last_error() { return g_blm_error; }
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, int width, int n_experts, int top,
-                                 int* __restrict__ ids, float* __restrict__ weights) {
+                                 int* __restrict__ ids, float* __restrict__ weights, int softmax, const float* __restrict__ correction,
+                                 int renorm) {
     extern __shared__ float smem[];
-    float* x = smem;                 // [width]
-    float* score = smem + width;     // [n_experts]
+    float* x = smem;                     // [width]
+    float* score = smem + width;         // [n_experts]: what a chosen expert is weighted by
+    float* choice = score + n_experts;   // [n_experts]: what the choice looks at (the score, plus the correction)
     const int n = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
     for (int d = threadIdx.x; d < width; d += blockDim.x) x[d] = to_f32(h[(size_t)n * width + d]);
@@ -31,15 +37,31 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
         for (int d = lane; d < width; d += 32) z = fmaf(w[d], x[d], z);
         z = warp_sum(z);
         // (a row of no sequence may hold anything, a NaN too: its score is 0, so that it still names experts that exist)
-        if (lane == 0) score[e] = z == z ? 1.0f / (1.0f + expf(-z)) : 0.f;
+        if (lane == 0) score[e] = softmax ? (z == z ? z : 0.f) : (z == z ? 1.0f / (1.0f + expf(-z)) : 0.f);
     }
     __syncthreads();
     if (warp == 0) {
+        if (softmax) {
+            float m = -INFINITY;
+            for (int e = lane; e < n_experts; e += 32) m = fmaxf(m, score[e]);
+            m = warp_max(m);
+            float sum = 0.f;
+            for (int e = lane; e < n_experts; e += 32) {
+                const float p = expf(score[e] - m);
+                score[e] = p;
+                sum += p;
+            }
+            sum = warp_sum(sum);
+            for (int e = lane; e < n_experts; e += 32) score[e] = score[e] / sum;
+        }
+        for (int e = lane; e < n_experts; e += 32) choice[e] = correction ? score[e] + correction[e] : score[e];
+        __syncwarp();
+        float total = 0.f;
         for (int k = 0; k < top; ++k) {
-            float best = -1.f;
+            float best = -INFINITY;
             int arg = 0x7fffffff;
             for (int e = lane; e < n_experts; e += 32) {
-                const float s = score[e];
+                const float s = choice[e];
                 if (s > best) { best = s; arg = e; }     // ascending e per lane: the lower index stays on a tie
             }
 #pragma unroll
@@ -48,26 +70,33 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
                 const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
                 if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
             }
+            if (arg == 0x7fffffff) arg = k;              // (scores that compare with nothing: still an expert that exists)
+            const float wgt = score[arg];
+            total += wgt;
             if (lane == 0) {
                 ids[(size_t)n * top + k] = arg;
-                weights[(size_t)n * top + k] = best;
-                score[arg] = -2.f;                       // taken
+                weights[(size_t)n * top + k] = wgt;
+                choice[arg] = -INFINITY;                 // taken
             }
             __syncwarp();
         }
+        if (renorm)
+            for (int k = lane; k < top; k += 32) weights[(size_t)n * top + k] = weights[(size_t)n * top + k] / (total + 1e-20f);
     }
 }
 
 BLM_API int blm_moe_route(const void* h, int dtype, const float* router, int n_tokens, int width, int n_experts, int top, int* ids,
-                          float* weights, cudaStream_t stream) {
+                          float* weights, int softmax, const float* correction, int renorm, cudaStream_t stream) {
     if (n_tokens == 0) return BLM_OK;
     BLM_REQUIRE(n_tokens > 0 && width > 0 && n_experts > 0 && top > 0 && top <= n_experts, "moe_route: bad sizes");
-    const size_t smem = ((size_t)width + n_experts) * sizeof(float);
+    const size_t smem = ((size_t)width + 2 * n_experts) * sizeof(float);
     BLM_REQUIRE(smem <= 48 * 1024, "moe_route: width %d and %d experts need %zu bytes of shared memory", width, n_experts, smem);
     if (dtype == BLM_F32)
-        moe_route_kernel<float><<<n_tokens, 128, smem, stream>>>((const float*)h, router, width, n_experts, top, ids, weights);
+        moe_route_kernel<float><<<n_tokens, 128, smem, stream>>>((const float*)h, router, width, n_experts, top, ids, weights, softmax,
+                                                                 correction, renorm);
     else if (dtype == BLM_BF16)
-        moe_route_kernel<__nv_bfloat16><<<n_tokens, 128, smem, stream>>>((const __nv_bfloat16*)h, router, width, n_experts, top, ids, weights);
+        moe_route_kernel<__nv_bfloat16><<<n_tokens, 128, smem, stream>>>((const __nv_bfloat16*)h, router, width, n_experts, top, ids,
+                                                                         weights, softmax, correction, renorm);
     else
         return blm_fail(BLM_BAD_ARGUMENT, "moe_route: dtype %d", dtype);
     return blm_check_launch("moe_route");
@@ -144,12 +173,24 @@ __device__ __forceinline__ bool moe_find_tile(const int* __restrict__ offsets, i
 // x rounded as the activations' dtype rounds it: the input of a product in that dtype
 template <typename T> __device__ __forceinline__ float as_input(float v) { return to_f32(from_f32<T>(v)); }
 
+// The gated unit of an expert.  limit <= 0: silu(g) * u.  limit > 0, the clamped unit: g = min(g, limit), u = clamp(u, -limit, limit),
+// g * sigmoid(alpha g) * (u + 1).
+struct GluAct {
+    float limit, alpha;
+};
+__device__ __forceinline__ float glu_act(float g, float u, GluAct a) {
+    if (a.limit <= 0.f) return g / (1.0f + expf(-g)) * u;
+    g = fminf(g, a.limit);
+    u = fminf(fmaxf(u, -a.limit), a.limit);
+    return g / (1.0f + expf(-a.alpha * g)) * (u + 1.0f);
+}
+
 // act[place, c] = silu(x . Wgate[e, c]) * (x . Wup[e, c]),  x = the pair's token row of h (times the pair's weight when
 // `scale_input`).  w_gu: [experts, 2 ff, width], an expert's gate rows followed by its up rows.
 template <typename T>
 __global__ void moe_gate_up_kernel(const T* __restrict__ h, const float* __restrict__ weights, const int* __restrict__ order,
                                    const int* __restrict__ offsets, const T* __restrict__ w_gu, T* __restrict__ act, int width, int ff,
-                                   int n_experts, int top, int scale_input) {
+                                   int n_experts, int top, int scale_input, GluAct glu) {
     __shared__ float xs[kBM][kBK + 1], gs[kBN][kBK + 1], us[kBN][kBK + 1];
     __shared__ int token_of[kBM];
     __shared__ float scale_of[kBM];
@@ -208,8 +249,7 @@ __global__ void moe_gate_up_kernel(const T* __restrict__ h, const float* __restr
         for (int j = 0; j < 2; ++j) {
             const int place = first + ty + 16 * i, c = c0 + tx + 16 * j;
             if (place < last && c < ff) {
-                const float g = ag[i][j];
-                act[(size_t)place * ff + c] = from_f32<T>(g / (1.0f + expf(-g)) * au[i][j]);
+                act[(size_t)place * ff + c] = from_f32<T>(glu_act(ag[i][j], au[i][j], glu));
             }
         }
 }
@@ -323,7 +363,7 @@ __device__ __forceinline__ void moe_warp_product2(float (&g)[8][4], float (&u)[8
 __global__ void __launch_bounds__(128) moe_gate_up_tc_kernel(const __nv_bfloat16* __restrict__ h, const float* __restrict__ weights,
                                                              const int* __restrict__ order, const int* __restrict__ offsets,
                                                              const __nv_bfloat16* __restrict__ w_gu, __nv_bfloat16* __restrict__ act,
-                                                             int width, int ff, int n_experts, int top, int scale_input) {
+                                                             int width, int ff, int n_experts, int top, int scale_input, GluAct glu) {
     extern __shared__ __align__(16) unsigned char moe_smem[];
     __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(moe_smem);      // 2 x (x, gate, up)
     __shared__ int token_of[kTM];
@@ -388,12 +428,12 @@ __global__ void __launch_bounds__(128) moe_gate_up_tc_kernel(const __nv_bfloat16
             if (p0 < last) {
                 const float x = s0 * g[j][0], y = s0 * g[j][1];
                 *reinterpret_cast<__nv_bfloat162*>(act + (size_t)p0 * ff + c) =
-                    __floats2bfloat162_rn(x / (1.0f + expf(-x)) * (s0 * u[j][0]), y / (1.0f + expf(-y)) * (s0 * u[j][1]));
+                    __floats2bfloat162_rn(glu_act(x, s0 * u[j][0], glu), glu_act(y, s0 * u[j][1], glu));
             }
             if (p1 < last) {
                 const float x = s1 * g[j][2], y = s1 * g[j][3];
                 *reinterpret_cast<__nv_bfloat162*>(act + (size_t)p1 * ff + c) =
-                    __floats2bfloat162_rn(x / (1.0f + expf(-x)) * (s1 * u[j][2]), y / (1.0f + expf(-y)) * (s1 * u[j][3]));
+                    __floats2bfloat162_rn(glu_act(x, s1 * u[j][2], glu), glu_act(y, s1 * u[j][3], glu));
             }
         }
     }
@@ -451,9 +491,11 @@ __global__ void __launch_bounds__(128) moe_down_tc_kernel(const __nv_bfloat16* _
 
 BLM_API int blm_moe_experts(const void* h, int dtype, const float* weights, const int* order, const int* offsets, const void* w_gu,
                             const void* w_down, void* act, float* y, int n_tokens, int width, int ff, int n_experts, int top,
-                            int scale_input, cudaStream_t stream) {
+                            int scale_input, float act_limit, float act_alpha, cudaStream_t stream) {
+    // act_limit <= 0: the experts' unit is silu(gate) * up; > 0: the clamped unit with that limit and act_alpha
     if (n_tokens == 0) return BLM_OK;
     BLM_REQUIRE(n_tokens > 0 && width > 0 && ff > 0 && n_experts > 0 && top > 0, "moe_experts: bad sizes");
+    const GluAct glu{act_limit, act_alpha};
     const long long pairs = (long long)n_tokens * top;
     const long long tiles = (pairs + kBM - 1) / kBM + n_experts;      // every expert's share may end in a tile that is not full
     BLM_REQUIRE(tiles < (1ll << 31), "moe_experts: %lld tiles", tiles);
@@ -461,7 +503,7 @@ BLM_API int blm_moe_experts(const void* h, int dtype, const float* weights, cons
     BLM_REQUIRE(g1.y <= 65535 && g2.y <= 65535, "moe_experts: too many output tiles");
     if (dtype == BLM_F32) {
         moe_gate_up_kernel<float><<<g1, 256, 0, stream>>>((const float*)h, weights, order, offsets, (const float*)w_gu, (float*)act, width,
-                                                          ff, n_experts, top, scale_input);
+                                                          ff, n_experts, top, scale_input, glu);
         moe_down_kernel<float><<<g2, 256, 0, stream>>>((const float*)act, offsets, (const float*)w_down, y, width, ff, n_experts);
     } else if (dtype == BLM_BF16 && width % 8 == 0 && ff % 8 == 0) {
         const long long t64 = (pairs + kTM - 1) / kTM + n_experts;
@@ -470,13 +512,13 @@ BLM_API int blm_moe_experts(const void* h, int dtype, const float* weights, cons
         cudaError_t err = cudaFuncSetAttribute(moe_gate_up_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1);
         if (err != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "moe_experts: %s", cudaGetErrorString(err));
         moe_gate_up_tc_kernel<<<t1, 128, smem1, stream>>>((const __nv_bfloat16*)h, weights, order, offsets, (const __nv_bfloat16*)w_gu,
-                                                          (__nv_bfloat16*)act, width, ff, n_experts, top, scale_input);
+                                                          (__nv_bfloat16*)act, width, ff, n_experts, top, scale_input, glu);
         moe_down_tc_kernel<<<t2, 128, smem2, stream>>>((const __nv_bfloat16*)act, offsets, (const __nv_bfloat16*)w_down, y, width, ff,
                                                        n_experts);
     } else if (dtype == BLM_BF16) {
         moe_gate_up_kernel<__nv_bfloat16><<<g1, 256, 0, stream>>>((const __nv_bfloat16*)h, weights, order, offsets,
                                                                   (const __nv_bfloat16*)w_gu, (__nv_bfloat16*)act, width, ff, n_experts,
-                                                                  top, scale_input);
+                                                                  top, scale_input, glu);
         moe_down_kernel<__nv_bfloat16><<<g2, 256, 0, stream>>>((const __nv_bfloat16*)act, offsets, (const __nv_bfloat16*)w_down, y, width,
                                                                ff, n_experts);
     } else {
@@ -488,9 +530,9 @@ BLM_API int blm_moe_experts(const void* h, int dtype, const float* weights, cons
 // ---------------------------------------------------------------------------------------------
 // out[n] = sum_k (weight_k if the weight is on the output) y[place_of[n, k]] + extra[n]   (k in the order of the choice)
 // ---------------------------------------------------------------------------------------------
-template <typename T>
+template <typename T, typename TO>
 __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place_of, const float* __restrict__ weights,
-                                   const T* __restrict__ extra, T* __restrict__ out, int width, int top, int scale_output) {
+                                   const T* __restrict__ extra, TO* __restrict__ out, int width, int top, int scale_output) {
     const int n = blockIdx.x;
     for (int d = threadIdx.x; d < width; d += blockDim.x) {
         float s = 0.f;
@@ -499,19 +541,25 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
             s += scale_output ? weights[(size_t)n * top + k] * v : v;
         }
         if (extra) s += to_f32(extra[(size_t)n * width + d]);
-        out[(size_t)n * width + d] = from_f32<T>(s);
+        out[(size_t)n * width + d] = from_f32<TO>(s);
     }
 }
 
 BLM_API int blm_moe_combine(const float* y, const int* place_of, const float* weights, const void* extra, void* out, int dtype,
-                            int n_tokens, int width, int top, int scale_output, cudaStream_t stream) {
+                            int n_tokens, int width, int top, int scale_output, int out_dtype, cudaStream_t stream) {
+    // dtype: that of `extra`; out_dtype: that of `out` (the same, or float32: the sum handed on unrounded)
     if (n_tokens == 0) return BLM_OK;
     BLM_REQUIRE(n_tokens > 0 && width > 0 && top > 0, "moe_combine: bad sizes");
-    if (dtype == BLM_F32)
-        moe_combine_kernel<float><<<n_tokens, 256, 0, stream>>>(y, place_of, weights, (const float*)extra, (float*)out, width, top, scale_output);
+    if (dtype == BLM_BF16 && out_dtype == BLM_F32)
+        moe_combine_kernel<__nv_bfloat16, float><<<n_tokens, 256, 0, stream>>>(y, place_of, weights, (const __nv_bfloat16*)extra,
+                                                                               (float*)out, width, top, scale_output);
+    else if (dtype != out_dtype)
+        return blm_fail(BLM_BAD_ARGUMENT, "moe_combine: dtype %d with out dtype %d", dtype, out_dtype);
+    else if (dtype == BLM_F32)
+        moe_combine_kernel<float, float><<<n_tokens, 256, 0, stream>>>(y, place_of, weights, (const float*)extra, (float*)out, width, top, scale_output);
     else if (dtype == BLM_BF16)
-        moe_combine_kernel<__nv_bfloat16><<<n_tokens, 256, 0, stream>>>(y, place_of, weights, (const __nv_bfloat16*)extra,
-                                                                        (__nv_bfloat16*)out, width, top, scale_output);
+        moe_combine_kernel<__nv_bfloat16, __nv_bfloat16><<<n_tokens, 256, 0, stream>>>(y, place_of, weights, (const __nv_bfloat16*)extra,
+                                                                                       (__nv_bfloat16*)out, width, top, scale_output);
     else
         return blm_fail(BLM_BAD_ARGUMENT, "moe_combine: dtype %d", dtype);
     return blm_check_launch("moe_combine");

@@ -31,7 +31,7 @@ __device__ __forceinline__ float sigmoid_f(float v) { return 1.0f / (1.0f + expf
 __device__ __forceinline__ float softplus_r(float v) { return fmaxf(v, 0.f) + log1pf(expf(-fabsf(v))); }
 
 // ---------------------------------------------------------------------------------------------
-// causal convolution per channel over time, then optionally silu
+// causal convolution per channel over time; act 1: then silu; act 2: the token's own input is added (y = x + conv(x))
 //   x [N, x_stride] (channels at x_col0 ..), taps [C, K] (the last column is the current token's), bias [C] or null
 //   carried inputs: hist [K - 1][C] per copy, hist[m] = the input at position start - (K - 1) + m
 // ---------------------------------------------------------------------------------------------
@@ -41,7 +41,7 @@ __global__ void conv_kernel(const float* __restrict__ x, long long x_stride, int
                             const int* __restrict__ token_seq, const int* __restrict__ cu_seqlens,
                             const int* __restrict__ slot_of_seq, const int* __restrict__ start_pos,
                             float* __restrict__ state, long long slot_stride, long long copy_stride, long long hist_off,
-                            int carry_here) {
+                            int carry_here, __nv_bfloat16* __restrict__ out_bf, long long out_bf_stride) {
     const int n = blockIdx.y;
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= channels) return;
@@ -49,6 +49,7 @@ __global__ void conv_kernel(const float* __restrict__ x, long long x_stride, int
     const int seq = token_seq[n];
     if (seq < 0) {           // a row of no sequence
         *o = 0.f;
+        if (out_bf) out_bf[(size_t)n * out_bf_stride + c] = __float2bfloat16(0.f);
         return;
     }
     const int i = n - cu_seqlens[seq];
@@ -64,7 +65,10 @@ __global__ void conv_kernel(const float* __restrict__ x, long long x_stride, int
         else v = hist[(size_t)(K - 1 + back) * channels + c];
         acc += taps[(size_t)c * K + (K - 1 - j)] * v;
     }
-    *o = act ? silu_f(acc) : acc;
+    if (act == 2) acc += x[(size_t)n * x_stride + x_col0 + c];      // the input itself joins what the taps give
+    const float res = act == 1 ? silu_f(acc) : acc;
+    *o = res;
+    if (out_bf) out_bf[(size_t)n * out_bf_stride + c] = __float2bfloat16(res);
     if (carry_here) {        // every sequence brings one token: its thread also moves the carried inputs on, into the other copy
         float* fresh = both + (size_t)((start + 1) & 1) * copy_stride;
         for (int m = 0; m < K - 1; ++m) {
@@ -109,7 +113,8 @@ BLM_API int blm_causal_conv(const float* x, long long x_stride, int x_col0, int 
                             int K, int act, float* out, long long out_stride, int out_col0, const int* token_seq,
                             const int* cu_seqlens, const int* slot_of_seq, const int* start_pos, int n_tokens, int n_seqs,
                             float* state, long long slot_stride, long long copy_stride, long long hist_off,
-                            int single_tokens, cudaStream_t stream) {
+                            int single_tokens, void* out_bf, long long out_bf_stride, cudaStream_t stream) {
+    // out_bf (may be null): the result once more as bfloat16 [N, out_bf_stride], channel c in column c
     if (n_tokens == 0) return BLM_OK;
     BLM_REQUIRE(channels > 0 && K >= 1 && K <= kMaxTaps, "causal_conv: %d taps; this kernel takes 1 to %d", K, kMaxTaps);
     BLM_REQUIRE(n_tokens <= 65535 && n_seqs <= 65535, "causal_conv: a step of %d rows; this kernel takes 65,535", n_tokens);
@@ -117,7 +122,7 @@ BLM_API int blm_causal_conv(const float* x, long long x_stride, int x_col0, int 
     dim3 grid((channels + threads - 1) / threads, n_tokens);
     conv_kernel<<<grid, threads, 0, stream>>>(x, x_stride, x_col0, channels, taps, bias, K, act, out, out_stride, out_col0,
                                               token_seq, cu_seqlens, slot_of_seq, start_pos, state, slot_stride, copy_stride,
-                                              hist_off, single_tokens && K > 1 ? 1 : 0);
+                                              hist_off, single_tokens && K > 1 ? 1 : 0, (__nv_bfloat16*)out_bf, out_bf_stride);
     int rc = blm_check_launch("causal_conv");
     if (rc != BLM_OK || K == 1 || single_tokens) return rc;
     dim3 grid2((channels + threads - 1) / threads, n_seqs);
@@ -330,6 +335,165 @@ __global__ void __launch_bounds__(kScanThreads)
     }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// token shift: every one of S mixes of a token's input with the input of the token before it,
+//     out[s][n] = x[n] + (x[n - 1] - x[n]) * mu[s]        (zeros before a sequence's first token)
+// x float32 [N, x_stride]; mu float32 [S][C]; out [S][N][C].  The last input of every sequence is carried in `state`
+// at hist_off, [C] per copy, as the convolution carries its inputs (it is the carried input of a convolution of two taps).
+// ---------------------------------------------------------------------------------------------
+template <typename TO>
+__global__ void shift_mix_kernel(const float* __restrict__ x, long long x_stride, int channels, const float* __restrict__ mu, int S,
+                                 TO* __restrict__ out, long long set_stride, const int* __restrict__ token_seq,
+                                 const int* __restrict__ cu_seqlens, const int* __restrict__ slot_of_seq,
+                                 const int* __restrict__ start_pos, float* __restrict__ state, long long slot_stride,
+                                 long long copy_stride, long long hist_off, int carry_here) {
+    const int n = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= channels) return;
+    const int seq = token_seq[n];
+    if (seq < 0) {           // a row of no sequence
+        for (int s = 0; s < S; ++s) out[(size_t)s * set_stride + (size_t)n * channels + c] = from_f32<TO>(0.f);
+        return;
+    }
+    const int i = n - cu_seqlens[seq];
+    const int start = start_pos[seq];
+    float* both = state + (size_t)slot_of_seq[seq] * slot_stride + hist_off;
+    const float cur = x[(size_t)n * x_stride + c];
+    float prev;
+    if (i > 0) prev = x[(size_t)(n - 1) * x_stride + c];
+    else if (start == 0) prev = 0.f;
+    else prev = both[(size_t)(start & 1) * copy_stride + c];
+    const float diff = prev - cur;
+    for (int s = 0; s < S; ++s)
+        out[(size_t)s * set_stride + (size_t)n * channels + c] = from_f32<TO>(fmaf(diff, mu[(size_t)s * channels + c], cur));
+    if (carry_here) both[(size_t)((start + 1) & 1) * copy_stride + c] = cur;
+}
+
+BLM_API int blm_shift_mix(const float* x, long long x_stride, int channels, const float* mu, int n_mixes, void* out, int out_dtype,
+                          const int* token_seq, const int* cu_seqlens, const int* slot_of_seq, const int* start_pos, int n_tokens,
+                          int n_seqs, float* state, long long slot_stride, long long copy_stride, long long hist_off,
+                          int single_tokens, cudaStream_t stream) {
+    if (n_tokens == 0) return BLM_OK;
+    BLM_REQUIRE(channels > 0 && n_mixes > 0, "shift_mix: bad sizes");
+    BLM_REQUIRE(n_tokens <= 65535 && n_seqs <= 65535, "shift_mix: a step of %d rows; this kernel takes 65,535", n_tokens);
+    const int threads = 128;
+    dim3 grid((channels + threads - 1) / threads, n_tokens);
+    const long long set_stride = (long long)n_tokens * channels;
+    if (out_dtype == BLM_F32)
+        shift_mix_kernel<float><<<grid, threads, 0, stream>>>(x, x_stride, channels, mu, n_mixes, (float*)out, set_stride, token_seq,
+                                                              cu_seqlens, slot_of_seq, start_pos, state, slot_stride, copy_stride,
+                                                              hist_off, single_tokens ? 1 : 0);
+    else if (out_dtype == BLM_BF16)
+        shift_mix_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(x, x_stride, channels, mu, n_mixes, (__nv_bfloat16*)out, set_stride,
+                                                                      token_seq, cu_seqlens, slot_of_seq, start_pos, state, slot_stride,
+                                                                      copy_stride, hist_off, single_tokens ? 1 : 0);
+    else
+        return blm_fail(BLM_BAD_ARGUMENT, "shift_mix: out dtype %d", out_dtype);
+    int rc = blm_check_launch("shift_mix");
+    if (rc != BLM_OK || single_tokens) return rc;
+    dim3 grid2((channels + threads - 1) / threads, n_seqs);
+    conv_carry_kernel<<<grid2, threads, 0, stream>>>(x, x_stride, 0, channels, 2, cu_seqlens, slot_of_seq, start_pos, state,
+                                                     slot_stride, copy_stride, hist_off);
+    return blm_check_launch("shift_mix (carry)");
+}
+
+// Linear attention with a decay per key channel.  Per head h, S [dk x dv]:
+//     read first (a bonus u for the current token):   o = (S + diag(u) k v^T)^T q;   S <- diag(w) S + k v^T
+//     read last:                                       S <- diag(w) S + k v^T;        o = S^T q
+// What the raw inputs mean is the kind:
+//     kDecayExpExp       w = exp(-exp(a + bias)),  q and k as they come            (bias [H dk]: the decays' base)
+//     kDecayLowerBound   w = low + (1 - low) sigmoid(a + bias),  k = 1 - w,  q = silu(q)     (extra [H dk]: low)
+// `extra` is the bonus u [H dk] when the state is read first.  AT as in the state-space scan: double holds the state and
+// the sums over its rows in float64 inside a step (the 32-bit path).
+constexpr int kDecayExpExp = 0, kDecayLowerBound = 1;
+
+template <int RN, int RG, bool READ_FIRST, typename AT>
+__global__ void __launch_bounds__(kScanThreads)
+    decay_scan_kernel(const float* __restrict__ q, long long q_stride, int q_col0, const float* __restrict__ k, long long k_stride,
+                      int k_col0, const float* __restrict__ v, long long v_stride, int v_col0, const float* __restrict__ a_raw,
+                      long long a_stride, int a_col0, const float* __restrict__ bias, const float* __restrict__ extra,
+                      float* __restrict__ o, long long o_stride, int heads, int dk, int dv, int kind,
+                      const int* __restrict__ cu_seqlens, const int* __restrict__ slot_of_seq, const int* __restrict__ start_pos,
+                      float* __restrict__ state, long long slot_stride, long long copy_stride, long long state_off) {
+    constexpr int NP = RN * RG, kCols = kScanThreads / RG, kRowGroups = RG;
+    extern __shared__ __align__(16) float sm[];
+    float* ks = sm;                          // [kChunk][NP]
+    float* qs = ks + kChunk * NP;            // [kChunk][NP]
+    float* ws = qs + kChunk * NP;            // [kChunk][NP]
+    float* vs = ws + kChunk * NP;            // [kChunk][kCols]
+    const int seq = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * kCols;
+    const ScanSeq sq = scan_seq(seq, cu_seqlens, slot_of_seq, start_pos, state, slot_stride, copy_stride, state_off);
+    if (sq.n_new <= 0) return;
+    const int tid = threadIdx.x, col = tid / kRowGroups, rg = tid % kRowGroups;
+    const bool live = col0 + col < dv;
+    const size_t head_off = (size_t)h * RN * dv * kRowGroups;
+    AT s[RN];
+    float ub[RN];
+#pragma unroll
+    for (int r = 0; r < RN; ++r) {
+        s[r] = (sq.read && live) ? (AT)sq.read[head_off + ((size_t)r * dv + col0 + col) * kRowGroups + rg] : (AT)0;
+        const int n = r * kRowGroups + rg;
+        ub[r] = (READ_FIRST && extra && n < dk) ? extra[h * dk + n] : 0.f;
+    }
+    for (int c0 = 0; c0 < sq.n_new; c0 += kChunk) {
+        const int nt = min(kChunk, sq.n_new - c0);
+        __syncthreads();
+        for (int e = tid; e < nt * NP; e += blockDim.x) {
+            const int t = e / NP, n = e % NP;
+            const size_t row = (size_t)(sq.first + c0 + t);
+            float kk = 0.f, qq = 0.f, w = 1.f;
+            if (n < dk) {
+                const float a = a_raw[row * a_stride + a_col0 + h * dk + n] + bias[h * dk + n];
+                qq = q[row * q_stride + q_col0 + h * dk + n];
+                if (kind == kDecayExpExp) {
+                    w = expf(-expf(a));
+                    kk = k[row * k_stride + k_col0 + h * dk + n];
+                } else {
+                    const float low = extra[h * dk + n];
+                    w = low + (1.0f - low) * sigmoid_f(a);
+                    kk = 1.0f - w;
+                    qq = silu_f(qq);
+                }
+            }
+            ks[e] = kk;
+            qs[e] = qq;
+            ws[e] = w;
+        }
+        for (int e = tid; e < nt * kCols; e += blockDim.x) {
+            const int t = e / kCols, p = e % kCols;
+            vs[e] = col0 + p < dv ? v[(size_t)(sq.first + c0 + t) * v_stride + v_col0 + h * dv + col0 + p] : 0.f;
+        }
+        __syncthreads();
+#pragma unroll 2
+        for (int t = 0; t < nt; ++t) {
+            const AT vv = (AT)vs[t * kCols + col];
+            const float* kk = ks + t * NP + rg;
+            const float* qq = qs + t * NP + rg;
+            const float* ww = ws + t * NP + rg;
+            AT part[4] = {0, 0, 0, 0};
+#pragma unroll
+            for (int r = 0; r < RN; ++r) {
+                const AT kv = (AT)kk[r * kRowGroups] * vv;
+                if (READ_FIRST) {
+                    part[r & 3] += (s[r] + (AT)ub[r] * kv) * (AT)qq[r * kRowGroups];
+                    s[r] = (AT)ww[r * kRowGroups] * s[r] + kv;
+                } else {
+                    s[r] = (AT)ww[r * kRowGroups] * s[r] + kv;
+                    part[r & 3] += s[r] * (AT)qq[r * kRowGroups];
+                }
+            }
+            AT acc = (part[0] + part[1]) + (part[2] + part[3]);
+            acc = group_sum<RG>(acc);
+            if (rg == 0 && live) o[(size_t)(sq.first + c0 + t) * o_stride + h * dv + col0 + col] = (float)acc;
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int r = 0; r < RN; ++r) sq.write[head_off + ((size_t)r * dv + col0 + col) * kRowGroups + rg] = (float)s[r];
+    }
+}
+
 static int row_groups(int) { return 8; }
 static int rows_per_thread(int n) {       // the smallest instance that holds n rows: row groups x RN
     for (int rn : {1, 2, 4, 8, 16, 32})
@@ -402,10 +566,49 @@ BLM_API int blm_delta_scan(const float* q, long long q_stride, int q_col0, const
     return blm_check_launch("delta_scan");
 }
 
+BLM_API int blm_decay_scan(const float* q, long long q_stride, int q_col0, const float* k, long long k_stride, int k_col0,
+                           const float* v, long long v_stride, int v_col0, const float* a_raw, long long a_stride, int a_col0,
+                           const float* bias, const float* extra, float* o, long long o_stride, int heads, int dk, int dv, int kind,
+                           int read_first, const int* cu_seqlens, const int* slot_of_seq, const int* start_pos, int n_seqs,
+                           float* state, long long slot_stride, long long copy_stride, long long state_off, int wide_sums,
+                           cudaStream_t stream) {
+    if (n_seqs == 0) return BLM_OK;
+    const int rn = rows_per_thread(dk);
+    BLM_REQUIRE(rn > 0, "decay_scan: keys of %d lanes; this kernel takes up to %d", dk, 32 * 8);
+    BLM_REQUIRE(heads > 0 && dv > 0 && heads <= 65535 && dv <= 65535 * 8, "decay_scan: bad head counts");
+    BLM_REQUIRE(kind == kDecayExpExp || kind == kDecayLowerBound, "decay_scan: kind %d", kind);
+    BLM_REQUIRE(kind != kDecayExpExp || k != nullptr, "decay_scan: this kind reads its keys");
+    BLM_REQUIRE(kind != kDecayLowerBound || (extra != nullptr && !read_first), "decay_scan: a lower bound, and the state read last");
+    const int rg = row_groups(dk), cols = kScanThreads / rg;
+    dim3 grid(n_seqs, heads, (dv + cols - 1) / cols);
+    const size_t smem = ((size_t)3 * kChunk * rn * rg + kChunk * cols) * sizeof(float);
+#define DECAY_ARGS q, q_stride, q_col0, k, k_stride, k_col0, v, v_stride, v_col0, a_raw, a_stride, a_col0, bias, extra, o, o_stride, heads, dk, dv, kind, cu_seqlens, slot_of_seq, start_pos, state, slot_stride, copy_stride, state_off
+#define BLM_ONE(RN, RG, FIRST, AT)                                                                       \
+    {                                                                                                    \
+        int rc = allow_smem(decay_scan_kernel<RN, RG, FIRST, AT>, smem, "decay_scan_kernel");            \
+        if (rc != BLM_OK) return rc;                                                                     \
+        decay_scan_kernel<RN, RG, FIRST, AT><<<grid, kScanThreads, smem, stream>>>(DECAY_ARGS);          \
+    }
+#define BLM_SCAN(RN, RG)                                                                                 \
+    if (rn == RN && rg == RG) {                                                                          \
+        if (read_first && wide_sums) BLM_ONE(RN, RG, true, double)                                       \
+        else if (read_first) BLM_ONE(RN, RG, true, float)                                                \
+        else if (wide_sums) BLM_ONE(RN, RG, false, double)                                               \
+        else BLM_ONE(RN, RG, false, float)                                                               \
+    }
+    BLM_SCAN(1, 8) BLM_SCAN(2, 8) BLM_SCAN(4, 8) BLM_SCAN(8, 8) BLM_SCAN(16, 8) BLM_SCAN(32, 8)
+#undef BLM_SCAN
+#undef BLM_ONE
+#undef DECAY_ARGS
+    return blm_check_launch("decay_scan");
+}
+
 // ---------------------------------------------------------------------------------------------
 // RMS norm over groups of a row's lanes, with a gate
 //   mode 0 (gate first):  u = y silu(gate);  out = u / sqrt(mean_group(u^2) + eps) * w[lane % period]
 //   mode 1 (gate last):   out = y / sqrt(mean_group(y^2) + eps) * w[lane % period] * sigmoid(gate)
+//   mode 2 (silu last):   out = y / sqrt(mean_group(y^2) + eps) * w[lane % period] * silu(gate)
+//   mode 3 (no gate):     out = y / sqrt(mean_group(y^2) + eps) * w[lane % period]            (gate may be null)
 // A warp per (row, group).  Rows of no sequence hold zeros and give zeros.
 // ---------------------------------------------------------------------------------------------
 template <typename TA>
@@ -415,7 +618,7 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, long long y
     const int n = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
     const float* yr = y + (size_t)n * y_stride;
-    const float* gr = gate + (size_t)n * gate_stride + gate_col0;
+    const float* gr = gate ? gate + (size_t)n * gate_stride + gate_col0 : nullptr;
     TA* orow = out + (size_t)n * out_stride;
     for (int g = warp; g < n_groups; g += n_warps) {
         const int lo = g * group;
@@ -429,9 +632,11 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, long long y
         const float inv = 1.0f / sqrtf(ss / (float)group + eps);
         for (int i = lane; i < group; i += 32) {
             float u = yr[lo + i];
-            const float gv = gr[lo + i];
+            const float gv = gr ? gr[lo + i] : 0.f;
             if (mode == 0) u = u * silu_f(gv) * inv * w[(lo + i) % period];
-            else u = u * inv * w[(lo + i) % period] * sigmoid_f(gv);
+            else if (mode == 1) u = u * inv * w[(lo + i) % period] * sigmoid_f(gv);
+            else if (mode == 2) u = u * inv * w[(lo + i) % period] * silu_f(gv);
+            else u = u * inv * w[(lo + i) % period];
             orow[lo + i] = from_f32<TA>(u);
         }
     }
@@ -441,7 +646,8 @@ BLM_API int blm_gated_group_norm(const float* y, long long y_stride, const float
                                  const float* w, int period, int group, int n_groups, int mode, float eps, void* out,
                                  int out_dtype, long long out_stride, int n, cudaStream_t stream) {
     if (n == 0) return BLM_OK;
-    BLM_REQUIRE(group > 0 && n_groups > 0 && period > 0 && (mode == 0 || mode == 1), "gated_group_norm: bad sizes or mode");
+    BLM_REQUIRE(group > 0 && n_groups > 0 && period > 0 && mode >= 0 && mode <= 3 && (gate != nullptr || mode == 3),
+                "gated_group_norm: bad sizes or mode");
     const int threads = n_groups >= 8 ? 256 : 32 * n_groups;
     if (out_dtype == BLM_F32)
         gated_group_norm_kernel<float><<<n, threads, 0, stream>>>(y, y_stride, gate, gate_stride, gate_col0, w, period, group,

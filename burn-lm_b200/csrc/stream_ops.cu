@@ -133,6 +133,7 @@ __global__ void bias_act_kernel(const TI* __restrict__ x, const float* __restric
         float z = to_f32(x[row + c]);
         if (bias) z += bias[c];
         if (kind == 1) z = z > 0.f ? ap * z * z + 0.5f * z : an * (expm1f(z) - z) + 0.5f * z;
+        else if (kind == 2) z = tanhf(z);
         out[row + c] = from_f32<TA>(z);
     }
 }
@@ -140,8 +141,8 @@ __global__ void bias_act_kernel(const TI* __restrict__ x, const float* __restric
 BLM_API int blm_bias_act(const void* x, int x_dtype, const float* bias, const float* params, void* out, int out_dtype, int n,
                          int width, int kind, cudaStream_t stream) {
     if (n == 0) return BLM_OK;
-    BLM_REQUIRE(n > 0 && width > 0 && (kind == 0 || kind == 1), "bias_act: bad sizes or kind");
-    BLM_REQUIRE(kind == 0 || params != nullptr, "bias_act: the activation needs its two numbers");
+    BLM_REQUIRE(n > 0 && width > 0 && (kind == 0 || kind == 1 || kind == 2), "bias_act: bad sizes or kind");
+    BLM_REQUIRE(kind != 1 || params != nullptr, "bias_act: the activation needs its two numbers");
     BLM_REQUIRE(n <= 65535, "bias_act: %d rows; this kernel takes 65,535", n);
     const int threads = 256;
     dim3 grid((width + threads - 1) / threads < 64 ? (width + threads - 1) / threads : 64, n);
@@ -171,4 +172,57 @@ BLM_API int blm_weighted_sum(const float* a, const float* b, float* out, float s
     const int blocks = (int)(want < 65535u * 16u ? want : 65535u * 16u);
     weighted_sum_kernel<<<blocks, threads, 0, stream>>>(a, b, out, sa, sb, total);
     return blm_check_launch("weighted_sum");
+}
+
+// ---------------------------------------------------------------------------------------------
+// columns of a wider row: dst[n, col0 + d] = src[n, d] (+ delta[n, d], the sum also stored into src), converted to dst's type.
+// Two calls lay the stream and another row side by side as the input of one product.  src float32 [N, D];
+// delta float32 or bfloat16 [N, D] or null; dst [N, dst_stride].
+// ---------------------------------------------------------------------------------------------
+template <typename TD, typename TO>
+__global__ void pack_cols_kernel(float* __restrict__ src, const TD* __restrict__ delta, TO* __restrict__ dst, long long dst_stride,
+                                 int col0, int width) {
+    const int n = blockIdx.y;
+    const int d = blockIdx.x * blockDim.x + threadIdx.x;
+    if (d >= width) return;
+    float v = src[(size_t)n * width + d];
+    if (delta) {
+        v += to_f32(delta[(size_t)n * width + d]);
+        src[(size_t)n * width + d] = v;
+    }
+    dst[(size_t)n * dst_stride + col0 + d] = from_f32<TO>(v);
+}
+
+BLM_API int blm_pack_cols(float* src, const void* delta, int delta_dtype, void* dst, int dst_dtype, long long dst_stride, int col0,
+                          int n_rows, int width, cudaStream_t stream) {
+    if (n_rows == 0) return BLM_OK;
+    BLM_REQUIRE(n_rows > 0 && n_rows <= 65535 && width > 0 && col0 >= 0 && col0 + width <= dst_stride, "pack_cols: bad sizes");
+    const int threads = 256;
+    dim3 grid((width + threads - 1) / threads, n_rows);
+#define BLM_PC(TD, TO) pack_cols_kernel<TD, TO><<<grid, threads, 0, stream>>>(src, (const TD*)delta, (TO*)dst, dst_stride, col0, width)
+    if (delta_dtype == BLM_F32 && dst_dtype == BLM_F32) BLM_PC(float, float);
+    else if (delta_dtype == BLM_F32 && dst_dtype == BLM_BF16) BLM_PC(float, __nv_bfloat16);
+    else if (delta_dtype == BLM_BF16 && dst_dtype == BLM_BF16) BLM_PC(__nv_bfloat16, __nv_bfloat16);
+    else if (delta_dtype == BLM_BF16 && dst_dtype == BLM_F32) BLM_PC(__nv_bfloat16, float);
+    else return blm_fail(BLM_BAD_ARGUMENT, "pack_cols: dtypes %d/%d", delta_dtype, dst_dtype);
+#undef BLM_PC
+    return blm_check_launch("pack_cols");
+}
+
+// ---------------------------------------------------------------------------------------------
+// x <- cap * tanh(x / cap) in place (fp32): logits squashed into (-cap, cap)
+// ---------------------------------------------------------------------------------------------
+__global__ void softcap_kernel(float* __restrict__ x, float cap, size_t total) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+        x[i] = cap * tanhf(x[i] / cap);
+}
+
+BLM_API int blm_softcap(float* x, float cap, size_t total, cudaStream_t stream) {
+    if (total == 0) return BLM_OK;
+    BLM_REQUIRE(cap > 0.f, "softcap: the cap must be positive");
+    const int threads = 256;
+    const size_t want = (total + threads - 1) / threads;
+    const int blocks = (int)(want < 65535u * 16u ? want : 65535u * 16u);
+    softcap_kernel<<<blocks, threads, 0, stream>>>(x, cap, total);
+    return blm_check_launch("softcap");
 }

@@ -72,7 +72,7 @@ def _need_cuda(*tensors):
 _protos = {
     "elementwise": {
         "blm_embed": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p],
-        "blm_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
+        "blm_add_rmsnorm": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
                             c_float, c_void_p],
         "blm_rope_append": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
                             c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p],
@@ -103,11 +103,18 @@ _protos = {
                               c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
         "blm_bias_act": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "blm_weighted_sum": [c_void_p, c_void_p, c_void_p, c_float, c_float, c_size_t, c_void_p],
+        "blm_pack_cols": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_void_p],
+        "blm_softcap": [c_void_p, c_float, c_size_t, c_void_p],
     },
     "recurrent": {
         "blm_causal_conv": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_longlong, c_int,
                             c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_longlong, c_longlong, c_longlong,
-                            c_int, c_void_p],
+                            c_int, c_void_p, c_longlong, c_void_p],
+        "blm_shift_mix": [c_void_p, c_longlong, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                          c_int, c_void_p, c_longlong, c_longlong, c_longlong, c_int, c_void_p],
+        "blm_decay_scan": [c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_int, c_void_p, c_longlong,
+                           c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                           c_void_p, c_int, c_void_p, c_longlong, c_longlong, c_longlong, c_int, c_void_p],
         "blm_ssm_scan": [c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p,
                          c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                          c_longlong, c_longlong, c_longlong, c_int, c_void_p],
@@ -126,12 +133,20 @@ _protos = {
                                   c_float, c_float, c_int, c_void_p],
         "blm_sigmoid_attention_takes": [c_int, c_int, c_int, c_int, c_int, c_int],
     },
+    "attention_latent": {
+        "blm_latent_prepare": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_float, c_void_p, c_int, c_void_p, c_void_p,
+                               c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                               c_void_p],
+        "blm_latent_attention": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                 c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+        "blm_sigmoid_gate": [c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_void_p],
+    },
     "moe": {
-        "blm_moe_route": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+        "blm_moe_route": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p],
         "blm_moe_group": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
         "blm_moe_experts": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                            c_int, c_int, c_int, c_int, c_void_p],
-        "blm_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                            c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
+        "blm_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     },
     "attention": {
         "blm_attention": [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
@@ -141,6 +156,8 @@ _protos = {
     "gemm": {
         "blm_gemm_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong,
                          c_longlong, c_void_p],
+        "blm_gemm_f32_batched": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
+                                 c_longlong, c_longlong, c_longlong, c_void_p],
     },
     "gemv": {
         "blm_gemv": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int,
@@ -254,17 +271,19 @@ def add_rmsnorm(resid, delta, gamma, eps, out, rows=None):
 
     rows is None: resid[n] += delta[n] (stored), out[n] = norm(resid[n]) * gamma for every row.
     rows given (int32 [R]): out[i] = norm(resid[rows[i]] + delta[rows[i]]) * gamma; resid unchanged.
-    delta may be None.  resid is fp32 [N, D]; delta and out have the activation dtype."""
+    delta may be None.  resid is fp32 [N, D]; delta and out have the activation dtype, or delta is float32 beside a
+    bfloat16 out (a sublayer's unrounded output).  out may be resid itself (float32): the stream normed in place."""
     _need_cuda(resid, delta, gamma, out, rows)
     d = resid.shape[-1]
     n_out = rows.numel() if rows is not None else resid.shape[0]
     if resid.dtype != torch.float32 or gamma.numel() != d or tuple(out.shape) != (n_out, d):
         raise KernelError("add_rmsnorm: resid float32 [N, D], gamma [D], out [rows, D]")
-    if delta is not None and (delta.dtype != out.dtype or delta.shape != resid.shape):
-        raise KernelError("add_rmsnorm: delta must match resid's shape and out's dtype")
+    if delta is not None and ((delta.dtype != out.dtype and delta.dtype != torch.float32) or delta.shape != resid.shape):
+        raise KernelError("add_rmsnorm: delta must match resid's shape and have out's dtype or float32")
     if rows is not None and rows.dtype != torch.int32:
         raise KernelError("add_rmsnorm: rows must be int32")
-    _call("elementwise", "blm_add_rmsnorm", _ptr(resid), _ptr(delta), _ptr(gamma), _code(gamma.dtype), _ptr(out),
+    _call("elementwise", "blm_add_rmsnorm", _ptr(resid), _ptr(delta), _code(delta.dtype) if delta is not None else _code(out.dtype),
+          _ptr(gamma), _code(gamma.dtype), _ptr(out),
           _code(out.dtype), _ptr(rows), n_out, d, c_float(eps), _stream())
 
 
@@ -407,23 +426,31 @@ def attention_sink(q, step, pool, block_table, out, n_heads, n_kv, key_dim, valu
           c_float(scale), 1 if sink else 0, _stream(), kernels=2 if n_splits > 1 else 1)
 
 
-def moe_route(h, router, top):
+def moe_route(h, router, top, softmax=False, correction=None, renormalise=False):
     """(ids int32 [N, top], weights float32 [N, top]): every token's `top` experts of largest sigmoid(router h), in
-    falling order (the lower index on a tie), with those scores.  router float32 [experts, D]; sums in float32."""
-    _need_cuda(h, router)
+    falling order (the lower index on a tie), with those scores.  router float32 [experts, D]; sums in float32.
+    `softmax`: the scores are softmax(router h) over all experts.  `correction` float32 [experts]: added to the scores for
+    the choice only; the weights stay the scores.  `renormalise`: the chosen weights are divided by their sum + 1e-20."""
+    _need_cuda(h, router, correction)
+    _f32(correction)
+    if correction is not None and correction.numel() != router.shape[0]:
+        raise KernelError("moe_route: the correction has a number per expert")
     n, d = h.shape
     if router.dtype != torch.float32 or router.dim() != 2 or router.shape[1] != d:
         raise KernelError("moe_route: the router is float32 [experts, D]")
     ids = torch.empty((n, top), dtype=torch.int32, device=h.device)
     weights = torch.empty((n, top), dtype=torch.float32, device=h.device)
-    _call("moe", "blm_moe_route", _ptr(h), _code(h.dtype), _ptr(router), n, d, router.shape[0], top, _ptr(ids), _ptr(weights), _stream())
+    _call("moe", "blm_moe_route", _ptr(h), _code(h.dtype), _ptr(router), n, d, router.shape[0], top, _ptr(ids), _ptr(weights),
+          1 if softmax else 0, _ptr(correction), 1 if renormalise else 0, _stream())
     return ids, weights
 
 
-def moe_experts(h, ids, weights, gate_up, down, extra=None, weight_on_input=True):
+def moe_experts(h, ids, weights, gate_up, down, extra=None, weight_on_input=True, clamp_limit=0.0, clamp_alpha=1.702, out_dtype=None):
     """sum over a token's chosen experts of expert(weight h) (`weight_on_input`) or of weight expert(h), plus `extra`
     [N, D] when given; expert(x) = down[e] (silu(gate[e] x) * (up[e] x)).  gate_up [experts, 2 ff, D] (an expert's
-    gate rows, then its up rows) and down [experts, D, ff] in h's dtype.  Returns [N, D] in h's dtype."""
+    gate rows, then its up rows) and down [experts, D, ff] in h's dtype.  Returns [N, D] in h's dtype, or in float32
+    (`out_dtype`).  `clamp_limit` > 0: the experts' unit is the clamped one, g = min(gate x, limit), u = clamp(up x, -limit,
+    limit), g sigmoid(clamp_alpha g) (u + 1)."""
     _need_cuda(h, ids, weights, gate_up, down, extra)
     n, d = h.shape
     top = ids.shape[1]
@@ -442,13 +469,13 @@ def moe_experts(h, ids, weights, gate_up, down, extra=None, weight_on_input=True
     place_of = torch.empty(pairs, dtype=torch.int32, device=dev)
     act = torch.empty((pairs, ff), dtype=h.dtype, device=dev)
     y = torch.empty((pairs, d), dtype=torch.float32, device=dev)
-    out = torch.empty((n, d), dtype=h.dtype, device=dev)
+    out = torch.empty((n, d), dtype=out_dtype or h.dtype, device=dev)
     stream = _stream()
     _call("moe", "blm_moe_group", _ptr(ids), pairs, e, _ptr(offsets), _ptr(order), _ptr(place_of), stream)
     _call("moe", "blm_moe_experts", _ptr(h), _code(h.dtype), _ptr(weights), _ptr(order), _ptr(offsets), _ptr(gate_up), _ptr(down),
-          _ptr(act), _ptr(y), n, d, ff, e, top, 1 if weight_on_input else 0, stream, kernels=2)
+          _ptr(act), _ptr(y), n, d, ff, e, top, 1 if weight_on_input else 0, c_float(clamp_limit), c_float(clamp_alpha), stream, kernels=2)
     _call("moe", "blm_moe_combine", _ptr(y), _ptr(place_of), _ptr(weights), _ptr(extra), _ptr(out), _code(h.dtype), n, d, top,
-          0 if weight_on_input else 1, stream)
+          0 if weight_on_input else 1, _code(out.dtype), stream)
     return out
 
 
@@ -605,6 +632,34 @@ def gemm_f32(x, w, out=None):
         raise KernelError("gemm_f32: out must be float32 [N, M]")
     _call("gemm", "blm_gemm_f32", _ptr(x), _ptr(w), _ptr(out), n, m, k, k, k, m, _stream())
     return out
+
+
+def batched_product(x, w, out=None, out_dtype=None):
+    """out[b] = x[b] w[b]^T for a batch of small products of one shape: x [B, N, K], w [B, M, K], out [B, N, M]; the
+    operands may be strided views (rows a fixed distance apart, unit stride along K and M).  float32 operands run this
+    package's FFMA product, true 32-bit; bfloat16 operands the library's batched product, as the plain products of a
+    prompt do, with a bfloat16 or (`out_dtype`) float32 result."""
+    _need = [t for t in (x, w, out) if t is not None]
+    for t in _need:
+        if not t.is_cuda:
+            raise KernelError("burn-lm_b200 kernels run on a CUDA device only; got a CPU tensor")
+    b, n, k = x.shape
+    m = w.shape[1]
+    if tuple(w.shape) != (b, m, k) or x.dtype != w.dtype:
+        raise KernelError("batched_product: x [B, N, K] and w [B, M, K] of one dtype")
+    if x.dtype == torch.float32:
+        if out is None:
+            out = torch.empty((b, n, m), dtype=torch.float32, device=x.device)
+        if out.dtype != torch.float32 or tuple(out.shape) != (b, n, m) or any(t.stride(2) != 1 for t in (x, w, out)):
+            raise KernelError("batched_product: float32 out [B, N, M]; unit stride along the last axis")
+        _call("gemm", "blm_gemm_f32_batched", _ptr(x), _ptr(w), _ptr(out), b, n, m, k, c_longlong(x.stride(1)), c_longlong(w.stride(1)),
+              c_longlong(out.stride(1)), c_longlong(x.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)), _stream())
+        return out
+    if out is not None:
+        return torch.bmm(x, w.transpose(1, 2), out=out)
+    if out_dtype is not None and out_dtype != x.dtype:
+        return torch.bmm(x, w.transpose(1, 2), out_dtype=out_dtype)
+    return torch.bmm(x, w.transpose(1, 2))
 
 
 EPI_STORE, EPI_SWIGLU, EPI_RESID_ADD, EPI_ROPE = 0, 1, 2, 3
@@ -982,12 +1037,13 @@ def sandwich_norm(resid, delta, post_weight, mult, eps_post, pre_weight, eps_pre
           c_float(eps_pre), _ptr(out), _code(out.dtype) if out is not None else F32, _ptr(rows), n_out, d, _stream())
 
 
-ACT_NONE, ACT_XIELU = 0, 1
+ACT_NONE, ACT_XIELU, ACT_TANH = 0, 1, 2
 
 
 def bias_act(x, bias, out, kind=ACT_NONE, params=None):
     """out = act(x + bias) row by row; x, out [N, D] (float32 or bfloat16), bias float32 [D] or None.  ACT_XIELU with
-    params = float32 [2] (p, q): z > 0: softplus(p) z^2 + z / 2; else (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2."""
+    params = float32 [2] (p, q): z > 0: softplus(p) z^2 + z / 2; else (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2.
+    ACT_TANH: tanh(z)."""
     _need_cuda(x, bias, out, params)
     _f32(bias, params)
     n, d = x.shape
@@ -1034,12 +1090,18 @@ def _cols(t, col0, width):
     return _ptr(t), c_longlong(t.stride(0)), int(col0)
 
 
-def causal_conv(x, x_col0, channels, taps, bias, out, out_col0, step, state, state_offset, silu=True):
+def causal_conv(x, x_col0, channels, taps, bias, out, out_col0, step, state, state_offset, silu=True, out_bf16=None, residual=False):
     """y_t = sum_k taps[:, k] x_(t - (K-1) + k) (+ bias) per channel over each sequence's time, then silu; zeros before a
     sequence's start.  x, out float32 [N, *] (the channels at x_col0 / out_col0); taps float32 [C, K]; the last K - 1
     inputs of every sequence are carried in `state` (float32 [slots, 2, floats]) at state_offset, [K - 1, C].  A step in
-    which every sequence brings one token (step.max_q_len == 1) moves the carried inputs on in the same launch."""
-    _need_cuda(taps, bias, state)
+    which every sequence brings one token (step.max_q_len == 1) moves the carried inputs on in the same launch.
+    `out_bf16` (bfloat16 [N, C]): the result once more, rounded, for a product that reads it.  `residual` (without silu):
+    y_t = x_t + the sum over the taps."""
+    if residual and silu:
+        raise KernelError("causal_conv: the input is added to the plain convolution, not to an activated one")
+    _need_cuda(taps, bias, state, out_bf16)
+    if out_bf16 is not None and (out_bf16.dtype != torch.bfloat16 or tuple(out_bf16.shape) != (step.n_tokens, channels)):
+        raise KernelError("causal_conv: out_bf16 is bfloat16 [N, C]")
     _f32(taps, bias)
     k = taps.shape[1]
     if tuple(taps.shape) != (channels, k) or (bias is not None and bias.numel() != channels):
@@ -1049,9 +1111,10 @@ def causal_conv(x, x_col0, channels, taps, bias, out, out_col0, step, state, sta
     if x.shape[0] != step.n_tokens or out.shape[0] != step.n_tokens:
         raise KernelError("causal_conv: a row per token of the step")
     single = getattr(step, "max_q_len", 0) == 1
-    _call("recurrent", "blm_causal_conv", xp, xs, xc, channels, _ptr(taps), _ptr(bias), k, 1 if silu else 0, op, os_, oc,
+    _call("recurrent", "blm_causal_conv", xp, xs, xc, channels, _ptr(taps), _ptr(bias), k, 2 if residual else (1 if silu else 0), op, os_, oc,
           _ptr(step.token_seq), _ptr(step.cu_seqlens), _ptr(step.slot_of_seq), _ptr(step.start_pos), step.n_tokens, step.n_seqs,
-          *_state_args(state, state_offset), 1 if single else 0, _stream(), kernels=2 if k > 1 and not single else 1)
+          *_state_args(state, state_offset), 1 if single else 0, _ptr(out_bf16), c_longlong(channels), _stream(),
+          kernels=2 if k > 1 and not single else 1)
 
 
 def ssm_scan(xbc, x_col0, b_col0, c_col0, dt, dt_col0, dt_bias, a_log, d_skip, y, heads, groups, n_state, value_dim, step, state,
@@ -1094,19 +1157,63 @@ def delta_scan(q, q_col0, k, k_col0, v, v_col0, b, b_col0, a, a_col0, dt_bias, a
           *_state_args(state, state_offset), _stream())
 
 
-GATE_FIRST, GATE_LAST = 0, 1
+def shift_mix(x, mu, out, step, state, state_offset):
+    """out[s, n] = x[n] + (x[n - 1] - x[n]) * mu[s]: every one of S mixes of a token's input with the input of the token
+    before it in its sequence (zeros before the first).  x float32 [N, C]; mu float32 [S, C]; out [S, N, C] in float32 or
+    bfloat16.  The last input of every sequence is carried in `state` (float32 [slots, 2, floats]) at state_offset, [C]."""
+    _need_cuda(x, mu, out, state)
+    _f32(x, mu)
+    n, c = x.shape
+    s = mu.shape[0]
+    if n != step.n_tokens or tuple(mu.shape) != (s, c) or tuple(out.shape) != (s, n, c):
+        raise KernelError("shift_mix: x [N, C], mu [S, C], out [S, N, C]")
+    single = getattr(step, "max_q_len", 0) == 1
+    _call("recurrent", "blm_shift_mix", _ptr(x), c_longlong(x.stride(0)), c, _ptr(mu), s, _ptr(out), _code(out.dtype),
+          _ptr(step.token_seq), _ptr(step.cu_seqlens), _ptr(step.slot_of_seq), _ptr(step.start_pos), n, step.n_seqs,
+          *_state_args(state, state_offset), 1 if single else 0, _stream(), kernels=1 if single else 2)
+
+
+DECAY_EXP_EXP, DECAY_LOWER_BOUND = 0, 1
+
+
+def decay_scan(q, q_col0, k, k_col0, v, v_col0, a, a_col0, bias, extra, out, heads, key_dim, value_dim, kind, read_first, step,
+               state, state_offset, wide_sums=False):
+    """Linear attention with a decay per key channel, per head with a state S [key_dim x value_dim]:
+    `read_first`: o = (S + diag(u) k v^T)^T q, then S <- diag(w) S + k v^T (u = `extra`, a bonus for the current token);
+    else S <- diag(w) S + k v^T, then o = S^T q.  DECAY_EXP_EXP: w = exp(-exp(a + bias)), q and k as given.
+    DECAY_LOWER_BOUND: w = low + (1 - low) sigmoid(a + bias) with low = `extra`, k = 1 - w (k is not read), q = silu(q).
+    q, k, a [heads x key_dim] and v [heads x value_dim] are column ranges of float32 [N, *] tensors; bias, extra float32
+    [heads * key_dim]; out float32 [N, heads * value_dim].  `wide_sums`: the state and the sums over its rows are held in
+    float64 inside a step (the 32-bit path)."""
+    _need_cuda(bias, extra, out, state)
+    _f32(bias, extra, out)
+    qa = _cols(q, q_col0, heads * key_dim)
+    ka = _cols(k, k_col0, heads * key_dim) if k is not None else (c_void_p(0), c_longlong(0), 0)
+    va = _cols(v, v_col0, heads * value_dim)
+    aa = _cols(a, a_col0, heads * key_dim)
+    if tuple(out.shape) != (step.n_tokens, heads * value_dim) or not out.is_contiguous() or bias.numel() != heads * key_dim:
+        raise KernelError("decay_scan: out float32 [N, heads * value_dim], bias [heads * key_dim]")
+    if extra is not None and extra.numel() != heads * key_dim:
+        raise KernelError("decay_scan: extra [heads * key_dim]")
+    _call("recurrent", "blm_decay_scan", *qa, *ka, *va, *aa, _ptr(bias), _ptr(extra), _ptr(out), c_longlong(out.stride(0)), heads,
+          key_dim, value_dim, int(kind), 1 if read_first else 0, _ptr(step.cu_seqlens), _ptr(step.slot_of_seq), _ptr(step.start_pos),
+          step.n_seqs, *_state_args(state, state_offset), 1 if wide_sums else 0, _stream())
+
+
+GATE_FIRST, GATE_LAST, GATE_SILU_LAST, GATE_NONE = 0, 1, 2, 3
 
 
 def gated_group_norm(y, gate, gate_col0, weight, group, mode, eps, out):
     """RMS norm over groups of `group` lanes of every row with a gate.  GATE_FIRST: u = y silu(gate), out = u / rms(u) *
-    weight; GATE_LAST: out = y / rms(y) * weight * sigmoid(gate).  weight float32 of a row's or of a group's size (then
+    weight; GATE_LAST: out = y / rms(y) * weight * sigmoid(gate); GATE_SILU_LAST: ... * silu(gate); GATE_NONE: no gate
+    (`gate` None).  weight float32 of a row's or of a group's size (then
     shared by the groups); y float32 [N, C]; the gate a column range of a float32 tensor; out [N, C]."""
     _need_cuda(y, weight, out)
     _f32(y, weight)
     n, c = y.shape
     if c % group or weight.numel() not in (c, group) or tuple(out.shape) != (n, c) or not y.is_contiguous() or not out.is_contiguous():
         raise KernelError("gated_group_norm: groups must divide the row; weight of a row's or a group's size")
-    gp, gs, gc = _cols(gate, gate_col0, c)
+    gp, gs, gc = _cols(gate, gate_col0, c) if gate is not None else (c_void_p(0), c_longlong(0), 0)
     _call("recurrent", "blm_gated_group_norm", _ptr(y), c_longlong(y.stride(0)), gp, gs, gc, _ptr(weight), weight.numel(), group,
           c // group, int(mode), c_float(eps), _ptr(out), _code(out.dtype), c_longlong(out.stride(0)), n, _stream())
 
@@ -1163,3 +1270,89 @@ def sigmoid_attention(q, pool, block_table, step, out, n_heads, n_kv, key_dim, v
           _ptr(step.cu_seqlens), _ptr(step.slot_of_seq), _ptr(step.start_pos), _ptr(step.token_seq), _ptr(talk), _ptr(head_bias),
           _ptr(out), _ptr(partial), n, step.n_seqs, step.max_q_len, n_heads, n_kv, key_dim, value_dim, PAGE, int(ranges),
           c_float(scale), c_float(softcap), 1 if scalar_only else 0, _stream(), kernels=2 if ranges > 1 else 1)
+
+
+# ------------------------------------------------------------------------------------------------
+# attention over a cached latent
+# ------------------------------------------------------------------------------------------------
+def latent_prepare(q_proj, down, c_weight, eps, freq, rot_dims, q_nope, q_rot, pool, block_table, step, n_heads, key_dim, rot_dim,
+                   rank):
+    """q_proj float32 [N, heads * (key_dim + rot_dim)] (every head's unrotated lanes, then its rotated ones) and down
+    float32 [N, rank + rot_dim]: q_nope [heads, N, key_dim] (the cache's dtype) takes the unrotated lanes, q_rot float32
+    [N, heads, rot_dim] the rotated ones turned by the token's position (lanes 2i, 2i + 1 by position * freq[i] for the first
+    rot_dims lanes; freq float64 [rot_dims / 2]); the first `rank` lanes of `down`, RMS-normed with c_weight, and its last
+    rot_dim lanes, turned likewise, go to the token's place in the paged cache ([pages, PAGE, rank + rot_dim])."""
+    _need_cuda(c_weight, freq, q_nope, q_rot, pool, block_table)
+    _f32(q_proj, down, c_weight, q_rot)
+    if not q_proj.is_cuda or not down.is_cuda or q_proj.stride(1) != 1 or down.stride(1) != 1:
+        raise KernelError("latent_prepare: q_proj and down are CUDA tensors (column ranges of a wider one will do)")
+    n = step.n_tokens
+    if tuple(q_proj.shape) != (n, n_heads * (key_dim + rot_dim)) or tuple(down.shape) != (n, rank + rot_dim) or c_weight.numel() != rank:
+        raise KernelError("latent_prepare: q_proj [N, heads * (key_dim + rot_dim)], down [N, rank + rot_dim], c_weight [rank]")
+    if q_nope.dtype != pool.dtype or tuple(q_nope.shape) != (n_heads, n, key_dim) or tuple(q_rot.shape) != (n, n_heads, rot_dim):
+        raise KernelError("latent_prepare: q_nope [heads, N, key_dim] in the cache's dtype, q_rot float32 [N, heads, rot_dim]")
+    if pool.numel() % (PAGE * (rank + rot_dim)):
+        raise KernelError("latent_prepare: the pool does not consist of pages [PAGE, rank + rot_dim]")
+    if rot_dims and (freq is None or freq.dtype != torch.float64 or freq.numel() != rot_dims // 2):
+        raise KernelError("latent_prepare: freq must be float64 [rot_dims / 2]")
+    _call("attention_latent", "blm_latent_prepare", _ptr(q_proj), c_longlong(q_proj.stride(0)), _ptr(down), c_longlong(down.stride(0)),
+          _ptr(c_weight), c_float(eps), _ptr(freq), int(rot_dims), _ptr(q_nope), _ptr(q_rot), _ptr(pool), _code(pool.dtype),
+          _ptr(step.token_seq), _ptr(step.token_pos), _ptr(step.slot_of_seq), _ptr(block_table), block_table.shape[1], n, n_heads,
+          key_dim, rot_dim, rank, PAGE, _stream())
+
+
+def latent_attention_scratch_floats(n_tokens, n_heads, rank, n_splits) -> int:
+    return n_splits * n_tokens * n_heads * (rank + 2) if n_splits > 1 else 0
+
+
+def latent_attention(q_lat, q_rot, pool, block_table, step, out, n_heads, rank, rot_dim, scale, n_splits=1, partial=None):
+    """Causal softmax attention of every new token's heads over its sequence's cached positions, each one key of rank +
+    rot_dim lanes shared by the heads, whose first `rank` lanes are the value: score = (q_lat . c + q_rot . k_rot) * scale.
+    q_lat float32 [heads, N, rank], q_rot float32 [N, heads, rot_dim]; out [heads, N, rank] in float32 or the cache's dtype
+    (rows of no sequence are left as they are).  `n_splits` > 1 cuts every row's keys over that many blocks (`partial`:
+    float32 scratch of latent_attention_scratch_floats) whose shares are merged in order."""
+    _need_cuda(q_lat, q_rot, pool, block_table, out, partial)
+    _f32(q_lat, q_rot, partial)
+    n = step.n_tokens
+    if tuple(q_lat.shape) != (n_heads, n, rank) or tuple(q_rot.shape) != (n, n_heads, rot_dim) or tuple(out.shape) != (n_heads, n, rank):
+        raise KernelError("latent_attention: q_lat and out [heads, N, rank], q_rot [N, heads, rot_dim]")
+    if n_splits > 1 and (partial is None or partial.numel() < latent_attention_scratch_floats(n, n_heads, rank, n_splits)):
+        raise KernelError("latent_attention: the workspace is too small for the key shares")
+    _call("attention_latent", "blm_latent_attention", _ptr(q_lat), _ptr(q_rot), _ptr(pool), _code(pool.dtype), _ptr(block_table),
+          block_table.shape[1], _ptr(step.cu_seqlens), _ptr(step.slot_of_seq), _ptr(step.start_pos), _ptr(step.token_seq), _ptr(out),
+          _code(out.dtype), _ptr(partial), n, step.n_seqs, step.max_q_len, n_heads, rank, rot_dim, PAGE, c_float(scale), int(n_splits),
+          _stream(), kernels=2 if n_splits > 1 else 1)
+
+
+def sigmoid_gate(o, gate, out):
+    """out = o * sigmoid(gate), element by element; o and out [N, C]; gate [N, C] in float32 or o's dtype, possibly a
+    column range of a wider tensor."""
+    _need_cuda(o, out)
+    if not gate.is_cuda or gate.dim() != 2 or gate.stride(1) != 1:
+        raise KernelError("sigmoid_gate: the gate is a CUDA tensor [N, C] with unit stride along its rows")
+    if o.dim() != 2 or o.shape != gate.shape or o.shape != out.shape or o.dtype != out.dtype:
+        raise KernelError("sigmoid_gate: o, gate and out [N, C]; out in o's dtype")
+    _call("attention_latent", "blm_sigmoid_gate", _ptr(o), _code(o.dtype), _ptr(gate), _code(gate.dtype), c_longlong(gate.stride(0)),
+          _ptr(out), o.shape[0], o.shape[1], _stream())
+
+
+# ------------------------------------------------------------------------------------------------
+# the stream beside another row; capped logits
+# ------------------------------------------------------------------------------------------------
+def pack_cols(src, delta, dst, col0):
+    """dst[:, col0 : col0 + D] = src (+ delta, the sum also stored into src), converted to dst's dtype.  src float32
+    [N, D]; delta float32 or bfloat16 [N, D] or None; dst [N, W] with W >= col0 + D."""
+    _need_cuda(src, delta, dst)
+    _f32(src)
+    n, d = src.shape
+    if dst.dim() != 2 or dst.shape[0] != n or col0 < 0 or col0 + d > dst.shape[1] or (delta is not None and delta.shape != src.shape):
+        raise KernelError("pack_cols: src [N, D], dst [N, W] with room for D columns at col0")
+    _call("stream_ops", "blm_pack_cols", _ptr(src), _ptr(delta), _code(delta.dtype) if delta is not None else F32, _ptr(dst),
+          _code(dst.dtype), c_longlong(dst.stride(0)), int(col0), n, d, _stream())
+
+
+def softcap(x, cap: float):
+    """x <- cap * tanh(x / cap) in place; x float32."""
+    _need_cuda(x)
+    _f32(x)
+    _call("stream_ops", "blm_softcap", _ptr(x), c_float(cap), c_size_t(x.numel()), _stream())

@@ -101,11 +101,11 @@ class GatedDelta(Part):
         proj = self.proj(x, out_dtype=torch.float32)                         # [N, q | k | v | b] in fp32
         dev = proj.device
         conv = torch.empty((n, self.conv_channels), dtype=torch.float32, device=dev)
-        K.causal_conv(proj, 0, self.conv_channels, self.taps, None, conv, 0, step, cache.state, 0, silu=True)
+        K.causal_conv(proj, 0, self.conv_channels, self.taps, None, conv, 0, step, cache.state, cache.state_offset, silu=True)
         wide = self.second(self.low(x, out_dtype=rt.dtype), out_dtype=torch.float32)      # [N, decays | gate] in fp32
         o = torch.zeros((n, self.vw), dtype=torch.float32, device=dev)                    # rows of no sequence stay zero
         K.delta_scan(conv, 0, conv, self.qk, conv, 2 * self.qk, proj, self.conv_channels, wide, 0, self.dt_bias, self.a_log, o,
-                     s.n_heads, s.qk_heads, s.key_dim, s.value_dim, step, cache.state, self.hist_floats)
+                     s.n_heads, s.qk_heads, s.key_dim, s.value_dim, step, cache.state, cache.state_offset + self.hist_floats)
         gated = torch.empty((n, self.vw), dtype=rt.dtype, device=dev)
         K.gated_group_norm(o, wide, s.n_heads * s.key_dim, self.norm_weight, s.value_dim, K.GATE_LAST, s.eps, gated)
         return self.o(gated, out_dtype=torch.float32)

@@ -85,10 +85,10 @@ class Mamba2(Part):
         n, inner, gn = step.n_tokens, self.inner, s.groups * s.state
         proj = self.proj(x, out_dtype=torch.float32)                       # [N, z | x | B | C | dt] in fp32
         xbc = torch.empty((n, self.conv_channels), dtype=torch.float32, device=proj.device)
-        K.causal_conv(proj, inner, self.conv_channels, self.taps, self.conv_bias, xbc, 0, step, cache.state, 0, silu=True)
+        K.causal_conv(proj, inner, self.conv_channels, self.taps, self.conv_bias, xbc, 0, step, cache.state, cache.state_offset, silu=True)
         y = torch.zeros((n, inner), dtype=torch.float32, device=proj.device)      # rows of no sequence stay zero
         K.ssm_scan(xbc, 0, inner, inner + gn, proj, 2 * inner + 2 * gn, self.dt_bias, self.a_log, self.d_skip, y,
-                   s.n_heads, s.groups, s.state, s.value_dim, step, cache.state, self.hist_floats, wide_sums=rt.exact)
+                   s.n_heads, s.groups, s.state, s.value_dim, step, cache.state, cache.state_offset + self.hist_floats, wide_sums=rt.exact)
         gated = torch.empty((n, inner), dtype=rt.dtype, device=proj.device)
         K.gated_group_norm(y, proj, 0, self.norm_weight, inner // s.norm_groups, K.GATE_FIRST, s.eps, gated)
         return self.o(gated, out_dtype=torch.float32)

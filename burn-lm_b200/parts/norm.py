@@ -54,10 +54,18 @@ class RMSNorm(Part):
     takes_handed_norm = True      # a product that writes the stream may leave this norm's input (parts.linear.NormHandoff)
     takes_post_normed = True      # `delta` may be a PostNormed: normed, scaled and added by this norm's kernel
 
-    def add_norm(self, resid, delta, rows=None, lazy=False, handoff=None):
+    def add_norm(self, resid, delta, rows=None, lazy=False, handoff=None, out_dtype=None):
         """`lazy`: the caller can take a norm that is not computed yet (parts.linear.NormedStream);
         it gets one when nothing has to be added into the stream first.  `handoff`: where the writer of
-        the stream may have left this norm's input."""
+        the stream may have left this norm's input.  `out_dtype` float32: the normed rows unrounded, for a reader
+        that works on them before a product does (`delta` is then float32 or None)."""
+        if out_dtype is not None and out_dtype != self.runtime.dtype:
+            if handoff is not None:
+                handoff.claim(resid, self.gamma)
+            n = rows.numel() if rows is not None else resid.shape[0]
+            out = torch.empty((n, self.spec.size), dtype=out_dtype, device=resid.device)
+            K.add_rmsnorm(resid, delta, self.gamma, self.spec.eps, out, rows)
+            return out
         if isinstance(delta, PostNormed):
             if handoff is not None:
                 handoff.claim(resid, self.gamma)          # nothing a product left fits a stream that changes now
