@@ -30,12 +30,12 @@ from .allocators import CacheError, CacheFull, ContextLengthExceeded, IdAllocato
 @dataclass
 class CacheView:
     """What one run of the schedule sees of the cache."""
-    kind: str                               # "kv", "state" or "none"
+    kind: str                               # "kv", "ids", "rows", "state" or "none"; several joined by '+' 
     writes: bool                            # False: the line belongs to an earlier run; read only
     pool: Optional[torch.Tensor] = None     # kv: [pages, 2, n_kv_heads, PAGE, head_dim]; with values of another size than
                                             # the keys [pages, n_kv_heads * PAGE * (head_dim + value_dim)], a page's keys
                                             # [n_kv_heads, PAGE, head_dim] followed by its values [n_kv_heads, PAGE, value_dim];
-                                            # ids: int32 [pages, PAGE]
+                                            # ids: int32 [pages, PAGE]; rows: [pages, PAGE, head_dim]
     block_table: Optional[torch.Tensor] = None   # kv: int32 [max_seqs, max_pages_per_seq]
     state: Optional[torch.Tensor] = None    # state: [max_seqs, *state_shape]
     state_offset: int = 0                   # floats of a state copy that lie before the reader's own (a block that keeps
@@ -49,6 +49,8 @@ class _KVGroup:
         self.need, self.runs = need, list(runs)
         if need.kind == "ids":
             self.pool = torch.zeros((len(runs), n_pages, PAGE), dtype=torch.int32, device=device)
+        elif need.kind == "rows":
+            self.pool = torch.empty((len(runs), n_pages, PAGE, need.head_dim), dtype=dtype, device=device)
         elif need.value_dim is None or need.value_dim == need.head_dim:
             self.pool = torch.empty((len(runs), n_pages, 2, need.n_kv_heads, PAGE, need.head_dim), dtype=dtype, device=device)
         else:
@@ -120,7 +122,7 @@ class Cache:
         for name, need in (named or {}).items():
             by_need.setdefault(need, []).append(("named", name))
         for need, runs in by_need.items():
-            if need.kind in ("kv", "ids"):
+            if need.kind in ("kv", "ids", "rows"):
                 # (a windowed group has storage of its own; the window is applied in the kernels, and the
                 # group gives the pages before it back as the sequence grows)
                 g = _KVGroup(need, runs, self.n_pages, max_seqs, self.max_pages_per_seq, dtype, device)
@@ -166,7 +168,7 @@ class Cache:
             raise CacheError(f"a run keeps two things of one kind: {kinds}")
         out = CacheView("+".join(kinds) if kinds else "none", views[0].writes)
         for v in views:
-            if v.kind in ("kv", "ids"):
+            if v.kind in ("kv", "ids", "rows"):
                 out.pool, out.block_table, out.window, out.keep_first = v.pool, v.block_table, v.window, v.keep_first
             elif v.kind == "state":
                 out.state = v.state

@@ -9,6 +9,7 @@ import torch
 from .config.reader import read_config_json
 from .parts.base import CacheNeed, Runtime
 from .parts.linear import NormHandoff
+from . import kernels as K
 from .plan import ModelPlan
 from .registry import architecture_of, part_class
 from .weights.loader import load_tensors
@@ -68,6 +69,7 @@ class Model:
         self.plan, self.runtime, self.config = plan, runtime, config
         self.embedding = _build(plan.embedding, "embedding", runtime)
         self.stream_position = _build(plan.stream_position, "position", runtime) if plan.stream_position is not None else None
+        self.stream_parts = [_build(p, "stream", runtime) for p in plan.stream_parts]
         self.layers = [Layer(lp, runtime) for lp in plan.layers]
         self.final_norm = _build(plan.final_norm, "norm", runtime)
         self.head = _build(plan.head, "head", runtime)
@@ -76,6 +78,7 @@ class Model:
     # -- weights ---------------------------------------------------------------------------------
     def parts(self):
         out = [self.embedding] + ([self.stream_position] if self.stream_position is not None else [])
+        out.extend(self.stream_parts)
         for layer in self.layers:
             out.extend(layer.parts())
         out.extend([self.final_norm, self.head])
@@ -153,8 +156,18 @@ class Model:
             self.embedding.forward(step.tokens, resid)
         if self.stream_position is not None:
             self.stream_position.on_embedding(resid, step)      # an encoding that is added to the stream
+        embedded = None
+        if any(getattr(p, "needs_embedding", False) for p in self.stream_parts):
+            # a part between the runs reads the embedding's output again: the layers rewrite the stream in place, so a copy
+            embedded = torch.empty_like(resid)
+            K.pack_cols(resid, None, embedded, 0)
         delta = None
         for run, entry in enumerate(schedule):
+            if entry.before is not None:
+                resid = self.stream_parts[entry.before].forward(resid, delta, embedded, step)
+                delta = None
+                if step.handoff is not None:
+                    step.handoff.expect(None)      # nothing left for a norm fits the new stream
             block = self.layers[entry.layer].block
             if hasattr(block, "first_norm"):
                 # the norm that reads the stream after this block: the next run's first, or the last norm

@@ -14,6 +14,11 @@ from .mamba2 import Mamba2, Mamba2Spec
 from .gated_delta import GatedDelta, GatedDeltaSpec
 from .sigmoid_attention import SigmoidAttention, SigmoidAttentionSpec
 from .parallel_mixers import ParallelMixers, ParallelMixersSpec
+from .filter import ShortConv, ShortConvSpec
+from .latent_attention import LatentAttention, LatentAttentionSpec
+from .hgrn2 import Hgrn2, Hgrn2Spec
+from .wkv import Wkv, WkvSpec
+from .stream import ConcatProjection, ConcatProjectionSpec
 
 __all__ = ["CacheNeed", "Part", "Runtime", "StepContext", "Linear", "RMSNorm", "RMSNormSpec", "Llama3Scaling",
            "NoPosition", "NoPositionSpec", "Rotary", "RotarySpec", "rotary_inverse_frequencies", "Attention",
@@ -21,4 +26,5 @@ __all__ = ["CacheNeed", "Part", "Runtime", "StepContext", "Linear", "RMSNorm", "
            "DynamicTanh", "DynamicTanhSpec", "PairEmbedding", "PairEmbeddingSpec", "Embedding", "EmbeddingSpec", "Head", "HeadSpec",
            "PostNormed", "PostRMSNorm", "PostRMSNormSpec", "BiasedMLP", "BiasedMLPSpec", "SandwichBlock", "ScaledEmbedding",
            "ScaledEmbeddingSpec", "Mamba2", "Mamba2Spec", "GatedDelta", "GatedDeltaSpec", "SigmoidAttention", "SigmoidAttentionSpec",
-           "ParallelMixers", "ParallelMixersSpec"]
+           "ParallelMixers", "ParallelMixersSpec", "ShortConv", "ShortConvSpec", "LatentAttention", "LatentAttentionSpec", "Hgrn2",
+           "Hgrn2Spec", "Wkv", "WkvSpec", "ConcatProjection", "ConcatProjectionSpec"]

@@ -49,6 +49,8 @@ class CacheNeed:
     kind "kv":    keys and values per position: n_kv_heads x head_dim each (values of `value_dim` lanes when
                   that is set and differs); `window` None keeps all positions, a number keeps that many of the
                   latest, and beside them the first `keep_first` positions of the sequence.
+    kind "rows":  one row of `head_dim` lanes per position in the compute dtype, shared by all heads (a latent that keys
+                  and values are made from), paged like keys and values; `window` as above.
     kind "ids":   one int32 per position (a token id, say), paged like keys and values; `window` as above.
     kind "state": a fixed-size block per sequence of `state_shape` in `state_dtype`, zero when a
                   sequence starts.

@@ -152,3 +152,63 @@ class SandwichBlock:
             return pending
         self.mixer_post.add(resid, pending)
         return None
+
+
+@register_part("block", "prenorm_filtered")
+class FilteredPreNormBlock:
+    """The pre-norm block with a filter over time between the first norm and the mixer: h = filter(norm1(x));
+    x <- x + mixer(h); x <- x + feed_forward(norm2(x)).  The layer may have no feed-forward.  The norm hands its rows on
+    unrounded (float32); the filter (family "filter") returns them filtered, in float32 and in the compute dtype, and the
+    mixer reads the one it asks for (`takes_float32_input`).  What the filter carries per sequence lies at the start of
+    the run's state block; a mixer with a state of its own finds it behind that (`state_offset` of its view), and a mixer
+    that keeps keys gets a state block beside its pages."""
+    family = "block"
+    graph_safe = True
+
+    NAMES = ("mixer_norm", "input_filter", "mixer", "feed_forward_norm", "feed_forward")
+
+    def __init__(self, parts: dict):
+        if not set(self.NAMES[:3]) <= set(parts) <= set(self.NAMES) or len(parts) not in (3, 5):
+            raise ValueError(f"the filtered pre-norm block arranges parts named {self.NAMES} (the last two may be absent); "
+                             f"the layer has {sorted(parts)}")
+        self.mixer_norm, self.filter, self.mixer = parts["mixer_norm"], parts["input_filter"], parts["mixer"]
+        self.feed_forward_norm, self.feed_forward = parts.get("feed_forward_norm"), parts.get("feed_forward")
+        self.kernel_modules = ("elementwise",)
+
+    def first_norm(self):
+        return self.mixer_norm
+
+    def cache_need(self):
+        from .base import CacheNeed
+        own = self.filter.state_floats()
+        need = self.mixer.cache_need()
+        needs = list(need) if isinstance(need, tuple) else [need]
+        states = [n for n in needs if n.kind == "state"]
+        if len(states) > 1:
+            raise ValueError("a mixer behind a filter keeps at most one state block")
+        if states:
+            st = states[0]
+            if len(st.state_shape) != 2 or st.state_shape[0] != 2 or st.state_dtype != "float32":
+                raise ValueError("a mixer behind a filter keeps its state as two float32 copies")
+            merged = CacheNeed("state", state_shape=(2, own + st.state_shape[1]))
+            rest = [n for n in needs if n.kind not in ("state", "none")]
+            return tuple(rest + [merged]) if rest else merged
+        rest = [n for n in needs if n.kind != "none"]
+        mine = CacheNeed("state", state_shape=(2, own))
+        return tuple(rest + [mine]) if rest else mine
+
+    def forward(self, resid, delta, step, cache_view, next_norm=None):
+        import dataclasses
+
+        import torch
+        if getattr(step, "handoff", None) is not None:
+            step.handoff.expect(None)          # no product of this block prepares a norm's input
+        h = self.mixer_norm.add_norm(resid, delta, out_dtype=torch.float32)
+        wide, rounded = self.filter.forward(h, step, cache_view.state, 0)
+        view = dataclasses.replace(cache_view, state_offset=self.filter.state_floats())
+        x = wide if getattr(self.mixer, "takes_float32_input", False) else rounded
+        a = self.mixer.forward(x, step, view)
+        if self.feed_forward is None:
+            return a
+        x = self.feed_forward_norm.add_norm(resid, a)
+        return self.feed_forward.forward(x, step)

@@ -152,3 +152,51 @@ class Head(Part):
 
     def forward(self, x):
         return self.linear(x, out_dtype=torch.float32)
+
+
+@dataclass(frozen=True)
+class NormedEmbeddingSpec:
+    vocab_size: int
+    hidden_size: int
+    eps: float
+
+
+@register_part("embedding", "normed_table")
+class NormedEmbedding(Part):
+    """x = table[token] / sqrt(mean(table[token]^2) + eps) * weight: the row, RMS-normed in fp32 where it lies in the stream."""
+    family = "embedding"
+    graph_safe = True
+    roles = ("table", "norm")
+    kernel_modules = ("elementwise",)
+
+    def tensor_specs(self):
+        s, t = self.spec, self.tensor_names
+        return [TensorSpec(t["table"], (s.vocab_size, s.hidden_size)),
+                TensorSpec(t["norm"], (s.hidden_size,), init="one_plus_normal:0.1")]
+
+    def bind(self, loaded):
+        self.table = loaded[self.tensor_names["table"]]
+        self.gamma = loaded[self.tensor_names["norm"]].to(torch.float32).contiguous()
+
+    def forward(self, tokens, out):
+        K.embed(tokens, self.table, out)
+        K.add_rmsnorm(out, None, self.gamma, self.spec.eps, out)
+
+
+@dataclass(frozen=True)
+class CappedHeadSpec:
+    vocab_size: int
+    hidden_size: int
+    cap: Optional[float] = None        # logits <- cap * tanh(logits / cap); None: as they are
+
+
+@register_part("head", "capped_linear")
+class CappedHead(Head):
+    """logits = x W^T in fp32, then squashed into (-cap, cap)."""
+    kernel_modules = ("elementwise", "stream_ops")
+
+    def forward(self, x):
+        logits = self.linear(x, out_dtype=torch.float32)
+        if self.spec.cap:
+            K.softcap(logits, self.spec.cap)
+        return logits

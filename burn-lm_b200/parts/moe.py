@@ -85,3 +85,54 @@ class SigmoidMoE(Part):
         return K.moe_experts(x, ids, weights, self.gate_up, self.down, extra=extra, weight_on_input=self.spec.weight_on == "input")
 
     adds_to_stream = True
+
+
+@dataclass(frozen=True)
+class RoutedMoESpec:
+    hidden_size: int
+    n_experts: int
+    top: int
+    expert_size: int
+    scores: str = "softmax"                # "softmax" over all experts, or "sigmoid" of every logit
+    correction: bool = False               # a stored number per expert joins the scores for the choice only
+    renormalise: bool = True               # the chosen weights are divided by their sum + 1e-20
+    clamp_limit: Optional[float] = None    # the experts' clamped unit: g = min(Wgate x, limit), u = clamp(Wup x, -limit, limit),
+    clamp_alpha: float = 1.702             # y = g sigmoid(alpha g) (u + 1); None: silu(g) u
+
+
+@register_part("feed_forward", "routed_moe")
+class RoutedMoE(SigmoidMoE):
+    """The mixture of experts with the router's options spelled out: scores s = softmax(W_router h) over all experts (or
+    sigmoids), the `top` experts of largest s (+ a stored correction that the weights do not see), weights s of the chosen,
+    optionally divided by their sum; out = sum weight_k expert_k(h), with the plain or the clamped gated unit.  Router
+    logits, scores and weights are fp32.  tensors: "router", "correction" (when the spec says so); "gate", "up", "down"
+    with {} where the expert's number stands."""
+    roles = ("router", "correction", "gate", "up", "down")
+    adds_to_stream = False
+
+    def __init__(self, spec, tensors, runtime):
+        Part.__init__(self, spec, tensors, runtime)
+        if spec.scores not in ("softmax", "sigmoid"):
+            raise ValueError(f"scores are 'softmax' or 'sigmoid', not {spec.scores!r}")
+        if not 1 <= spec.top <= spec.n_experts:
+            raise ValueError(f"top {spec.top} of {spec.n_experts} experts")
+        self.shared = None
+
+    def tensor_specs(self):
+        specs = super().tensor_specs()
+        if self.spec.correction:
+            specs.insert(1, TensorSpec(self.tensor_names["correction"], (self.spec.n_experts,), init="normal:0.05"))
+        return specs
+
+    def bind(self, loaded):
+        super().bind(loaded)
+        self.correction = None
+        if self.spec.correction:
+            self.correction = loaded[self.tensor_names["correction"]].to(torch.float32).contiguous()
+
+    def forward(self, x, step):
+        s = self.spec
+        ids, weights = K.moe_route(x, self.router, s.top, softmax=s.scores == "softmax", correction=self.correction,
+                                   renormalise=s.renormalise)
+        return K.moe_experts(x, ids, weights, self.gate_up, self.down, weight_on_input=False, clamp_limit=s.clamp_limit or 0.0,
+                             clamp_alpha=s.clamp_alpha, out_dtype=torch.float32)

@@ -62,6 +62,7 @@ class ScheduleEntry:
     of writing a line of its own."""
     layer: int
     cache_of: Optional[int] = None
+    before: Optional[int] = None     # index among the plan's `stream_parts` of the part that rewrites the stream right before this run
 
 
 @dataclass(frozen=True)
@@ -80,11 +81,14 @@ class ModelPlan:
     duplicate_tensors: tuple = ()   # (stored name, wanted name) pairs: a stored tensor that may be there as a second copy
                                     # of a wanted one (a tied head written out); it must hold the same values
     stream_position: Optional[PartPlan] = None   # family "position": an encoding added to the stream after the embedding
+    stream_parts: tuple = ()        # of PartPlan, family "stream": rewrites of the stream that schedule entries name (`before`)
 
     def __post_init__(self):
         for n, e in enumerate(self.schedule):
             if not 0 <= e.layer < len(self.layers):
                 raise ValueError(f"schedule entry {n} names layer {e.layer}; there are {len(self.layers)}")
+            if e.before is not None and not 0 <= e.before < len(self.stream_parts):
+                raise ValueError(f"schedule entry {n} names stream part {e.before}; there are {len(self.stream_parts)}")
             if e.cache_of is not None:
                 if not 0 <= e.cache_of < n:
                     raise ValueError(f"schedule entry {n} reads the cache of entry {e.cache_of}, "

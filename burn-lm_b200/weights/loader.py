@@ -38,7 +38,7 @@ class TensorSpec:
     name: str
     shape: tuple
     kind: str = "float"          # "float" or "int"
-    init: str = "normal:0.02"    # for the random-weights mode: "normal:<std>" or "one_plus_normal:<std>"
+    init: str = "normal:0.02"    # for the random-weights mode: "normal:<std>", "one_plus_normal:<std>" or "sigmoid_normal:<std>"
     optional: bool = False       # a tensor the format stores but the part does not read: loaded when it is there,
                                  # not missed when it is not (the random-weights mode writes it)
     free: int = 0                # a dimension given as -1 is read off the stored tensor (a size that no configuration key

@@ -39,6 +39,8 @@ def random_tensor(spec, seed: int, dtype: torch.dtype, device="cpu") -> torch.Te
     t.normal_(0.0, std, generator=g)
     if kind == "one_plus_normal":
         t += 1.0
+    elif kind == "sigmoid_normal":      # numbers between 0 and 1 (a mixing weight, a lower bound of a gate)
+        t = torch.sigmoid(t)
     elif kind != "normal":
         raise ValueError(f"tensor {spec.name!r}: unknown initialiser {spec.init!r}")
     return t.to(dtype)
