@@ -111,6 +111,33 @@ _PRESETS["nufolix_tiny"] = {
 }
 
 
+def _ridopel_experts(n, top, ff, limit):
+    return {"kind": "moe", "expert": {"ff": ff, "limit": limit}, "router": {"experts": n, "top": top}}
+
+
+def _ridopel_latent(heads, dim, rot_dim, rot_dims, vdim, rank, scale, base, mlp):
+    return {"type": "latent_attention", "mlp": mlp,
+            "mixer": {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": rank, "scale": scale,
+                      "rot": {"dims": rot_dims, "base": base}}}
+
+
+# a small Ridopel decoder that uses every branch of the design: the three kinds of mixer with and without a
+# feed-forward, a loop over two layers of different kinds that starts behind the first layer, fewer turning lanes than
+# rotated ones, values wider and narrower than the keys, a cap on the logits
+_PRESETS["ridopel_tiny"] = {
+    "architecture": "Ridopel", "vocab": 352, "width": 96, "norm": {"eps": 1e-5}, "canon": {"taps": 4}, "logit_softcap": 20.0,
+    "loop": {"start": 1, "stop": 3, "times": 2},
+    "layers": [
+        {"type": "hgrn2", "mixer": {"heads": 3, "dim": 16, "vdim": 32}, "mlp": _ridopel_experts(8, 2, 48, 1.5)},
+        _ridopel_latent(4, 24, 16, 8, 20, 40, 0.17, 10000.0, _ridopel_experts(6, 3, 32, 1.0)),
+        {"type": "wkv", "mixer": {"heads": 3, "dim": 32}, "mlp": None},
+        _ridopel_latent(2, 16, 8, 8, 48, 24, 0.2, 5000.0, None),
+        {"type": "hgrn2", "mixer": {"heads": 2, "dim": 24, "vdim": 16}, "mlp": None},
+        {"type": "wkv", "mixer": {"heads": 2, "dim": 16}, "mlp": _ridopel_experts(4, 1, 64, 2.0)},
+    ],
+}
+
+
 def preset_names() -> list:
     return sorted(_PRESETS)
 
