@@ -1,7 +1,7 @@
 """Decode and prefill throughput of the Llama-3.2-1B shape with random weights on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--config 1b|3b|8b]
-    python bench.py --compare fobilorn|nufolix [--size 1b-layers|8b-layers]     (another design beside this one, see run_compare)
+    python bench.py --compare fobilorn|nufolix|ridopel [--size 1b-layers|8b-layers]     (another design beside this one, see run_compare)
 
 A "step" is one decode step of the whole batch.  The default run has the layer sizes of the 1B
 configuration (16 layers, width 2048, 32 heads on 8 kv heads of 64, inner 8192, vocabulary 128256,
@@ -495,10 +495,137 @@ def nufolix_kernels(z, pk):
     return out
 
 
+def ridopel_configs(z):
+    """(llama, ridopel) of one size.  The new design's layers take turns: attention over a cached latent (Llama's head count,
+    a latent of 4 heads' width, half a head rotated), WKV and HGRN2 with heads of Llama's size, each with `experts` experts of
+    which a token uses `top`, whose inner sizes make Llama's together."""
+    llama = compare_configs(z)["llama"]
+    hd, d, H = z["hd"], z["width"], z["heads"]
+    mlp = {"kind": "moe", "router": {"experts": z["experts"], "top": z["top"]}, "expert": {"ff": z["inner"] // z["top"], "limit": 7.0}}
+    latent = {"type": "latent_attention", "mlp": mlp,
+              "mixer": {"heads": H, "dim": hd, "rot_dim": hd // 2, "vdim": hd, "kv_rank": 4 * hd, "scale": (1.5 * hd) ** -0.5,
+                        "rot": {"dims": hd // 2, "base": 500000.0}}}
+    wkv = {"type": "wkv", "mlp": mlp, "mixer": {"heads": d // hd, "dim": hd}}
+    hgrn = {"type": "hgrn2", "mlp": mlp, "mixer": {"heads": d // hd, "dim": hd, "vdim": hd}}
+    turn = (latent, wkv, hgrn, latent)
+    rid = {"architecture": "Ridopel", "vocab": z["vocab"], "width": d, "norm": {"eps": 1e-6}, "canon": {"taps": 4}, "logit_softcap": 30.0,
+           "layers": [turn[i % 4] for i in range(z["layers"])]}
+    return {"llama": llama, "ridopel": rid}
+
+
+def ridopel_kernels(z, pk):
+    """The new design's kernels alone, CUDA events, back to back: attention over the latent beside the dense decoder's
+    attention (one 2,048-token prompt; 64 sequences of 1,088 tokens), the two decay scans over the same rows, and the clamped
+    experts beside dense products of the inner size a token uses."""
+    import torch
+    from types import SimpleNamespace
+    from burn_lm_b200 import kernels as K
+    dev, bf = "cuda", torch.bfloat16
+    H, G, hd, d = z["heads"], z["kv"], z["hd"], z["width"]
+    R, dr = 4 * hd, hd // 2
+    out = {}
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+
+    def step(n_seqs, new, cached):
+        seq = [s for s in range(n_seqs) for _ in range(new)]
+        pos = [cached + t for _ in range(n_seqs) for t in range(new)]
+        return SimpleNamespace(token_seq=i32(seq), token_pos=i32(pos), slot_of_seq=i32(list(range(n_seqs))),
+                               cu_seqlens=i32([new * s for s in range(n_seqs + 1)]), start_pos=i32([cached] * n_seqs),
+                               n_tokens=n_seqs * new, n_seqs=n_seqs, max_q_len=new, max_kv_len=cached + new)
+
+    def attention_case(n_seqs, new, cached):
+        total = cached + new
+        pages_each = -(-total // K.PAGE)
+        n = n_seqs * new
+        bt = torch.arange(n_seqs * pages_each, dtype=torch.int32, device=dev).reshape(n_seqs, pages_each)
+        st = step(n_seqs, new, cached)
+        q = torch.randn((n, H * hd), dtype=bf, device=dev)
+        pool5 = torch.randn((n_seqs * pages_each, 2, G, K.PAGE, hd), dtype=bf, device=dev)
+        o = torch.empty_like(q)
+        ms_llama = _time(lambda: K.attention(q, q.shape[1], pool5, bt, st.cu_seqlens, st.slot_of_seq, st.start_pos, o, n, n_seqs, new,
+                                             H, G, hd, hd ** -0.5, window=0, n_splits=1, max_kv_len=total))
+        # the key shares the mixer takes at this size (parts.latent_attention.LatentAttention._splits)
+        tiles = (new * H + 15) // 16 * n_seqs
+        splits = max(1, min(-(-2 * K.sm_count() // tiles), total // (2 * K.PAGE), 32))
+        pool = torch.randn((n_seqs * pages_each, K.PAGE, R + dr), dtype=bf, device=dev)
+        q_lat = torch.randn((H, n, R), dtype=torch.float32, device=dev) * 0.1
+        q_rot = torch.randn((n, H, dr), dtype=torch.float32, device=dev)
+        mixed = torch.empty((H, n, R), dtype=bf, device=dev)
+        partial = None
+        if splits > 1:
+            partial = torch.empty(K.latent_attention_scratch_floats(n, H, R, splits), dtype=torch.float32, device=dev)
+        ms_new = _time(lambda: K.latent_attention(q_lat, q_rot, pool, bt, st, mixed, H, R, dr, (1.5 * hd) ** -0.5, n_splits=splits,
+                                                  partial=partial), reps=3)
+        return ms_llama, ms_new, total, splits
+
+    ms_l, ms_n, total, splits = attention_case(1, 2048, 0)
+    pairs = 2048 * 2049 / 2
+    flops_l, flops_n = 4.0 * H * hd * pairs, 2.0 * H * (2 * R + dr) * pairs        # the latent is key and value of every head
+    out["attention_prefill_2048"] = {"llama_ms": round(ms_l, 4), "ridopel_ms": round(ms_n, 4), "key_shares": splits,
+                                     "llama_gflop": round(flops_l / 1e9, 1), "ridopel_gflop": round(flops_n / 1e9, 1),
+                                     "llama_frac_bf16": round(flops_l / (ms_l / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
+                                     "ridopel_frac_bf16": round(flops_n / (ms_n / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+    ms_l, ms_n, total, splits = attention_case(64, 1, 1087)
+    bytes_l, bytes_n = 64 * G * total * 2 * hd * 2, 64 * total * (R + dr) * 2
+    out["attention_decode_b64"] = {"llama_ms": round(ms_l, 4), "ridopel_ms": round(ms_n, 4), "keys_seen": total, "key_shares": splits,
+                                   "llama_mb": round(bytes_l / 1e6, 1), "ridopel_mb": round(bytes_n / 1e6, 1),
+                                   "llama_frac_hbm": round(bytes_l / (ms_l / 1e3) / 1e9 / pk["hbm_gbs"], 4),
+                                   "ridopel_frac_hbm": round(bytes_n / (ms_n / 1e3) / 1e9 / pk["hbm_gbs"], 4)}
+    # the scans: prompts read and write rows, single tokens the states
+    heads = d // hd
+    for name, kind, first in (("wkv", K.DECAY_EXP_EXP, True), ("hgrn2", K.DECAY_LOWER_BOUND, False)):
+        for n_seqs, new, cached in ((1, 2048, 0), (64, 1, 1087)):
+            st = step(n_seqs, new, cached)
+            n = st.n_tokens
+            floats = K.scan_state_floats(heads, hd, hd)
+            state = torch.zeros((n_seqs, 2, floats), dtype=torch.float32, device=dev)
+            rows = torch.randn((n, 4 * heads * hd), dtype=torch.float32, device=dev)
+            bias, extra = torch.zeros(heads * hd, dtype=torch.float32, device=dev), torch.full((heads * hd,), 0.5, dtype=torch.float32, device=dev)
+            y = torch.zeros((n, heads * hd), dtype=torch.float32, device=dev)
+            ms = _time(lambda: K.decay_scan(rows, 0, rows if first else None, heads * hd, rows, 2 * heads * hd, rows, 3 * heads * hd, bias,
+                                            extra, y, heads, hd, hd, kind, first, st, state, 0), reps=3)
+            row_bytes = 4.0 * n * heads * hd * (5 if first else 4)
+            state_bytes = 2.0 * 4 * n_seqs * floats
+            flops = 4.0 * n * heads * hd * hd
+            out[f"{name}_scan_{n_seqs}x{new}"] = {"ms": round(ms, 4), "frac_hbm": round((row_bytes + state_bytes) / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4),
+                                                  "gflop_fp32_per_s": round(flops / (ms / 1e3) / 1e9, 1)}
+    # feed-forward: a token's experts with the clamped unit beside dense products of the inner size they make together
+    E, top = z["experts"], z["top"]
+    each = z["inner"] // top
+    gate_up = torch.randn((E, 2 * each, d), dtype=bf, device=dev) * 0.02
+    down = torch.randn((E, d, each), dtype=bf, device=dev) * 0.02
+    router = torch.randn((E, d), dtype=torch.float32, device=dev)
+    correction = torch.randn(E, dtype=torch.float32, device=dev) * 0.05
+    w1 = torch.randn((2 * top * each, d), dtype=bf, device=dev) * 0.02
+    w2 = torch.randn((d, top * each), dtype=bf, device=dev) * 0.02
+    for n in (2048, 64):
+        h = torch.randn((n, d), dtype=bf, device=dev)
+        ms_route = _time(lambda: K.moe_route(h, router, top, softmax=True, correction=correction, renormalise=True))
+        ids, weights = K.moe_route(h, router, top, softmax=True, correction=correction, renormalise=True)
+        ms_moe = _time(lambda: K.moe_experts(h, ids, weights, gate_up, down, weight_on_input=False, clamp_limit=7.0, clamp_alpha=1.702,
+                                             out_dtype=torch.float32))
+        a = torch.empty((n, top * each), dtype=bf, device=dev)
+
+        def dense():
+            gu = torch.mm(h, w1.t())
+            K.swiglu(gu, a)
+            return torch.mm(a, w2.t())
+        ms_dense = _time(dense)
+        flops = 2.0 * n * top * 3 * each * d
+        wbytes = 2.0 * 3 * each * d * min(E, n * top)
+        out[f"experts_{n}_tokens"] = {
+            "route_ms": round(ms_route, 4), "ridopel_ms": round(ms_moe, 4), "dense_same_inner_ms": round(ms_dense, 4),
+            "ridopel_frac_bf16": round(flops / (ms_moe / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
+            "dense_frac_bf16": round(flops / (ms_dense / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
+            "ridopel_frac_hbm": round(wbytes / (ms_moe / 1e3) / 1e9 / pk["hbm_gbs"], 4),
+            "dense_frac_hbm": round(2.0 * 3 * top * each * d / (ms_dense / 1e3) / 1e9 / pk["hbm_gbs"], 4)}
+    return out
+
+
 def run_compare(args):
     """One JSON line per size and model: prefill of one 2,048-token prompt and decode at batch 8 and 64 after 512-token
-    prompts, for the dense Llama decoder and the Fobilorn decoder (dense feed-forwards, and experts) at equal layer
-    sizes with random weights; then a line with the kernels alone."""
+    prompts, for the dense Llama decoder and the named design (Fobilorn with dense feed-forwards and with experts, Nufolix,
+    Ridopel) at equal layer sizes with random weights; then a line with the kernels alone."""
     import torch
     import burn_lm_b200 as blm
     if not torch.cuda.is_available():
@@ -508,7 +635,9 @@ def run_compare(args):
     for size, z in COMPARE_SIZES.items():
         if args.size and size != args.size:
             continue
-        configs = nufolix_configs(z) if args.compare == "nufolix" else compare_configs(z)
+        if args.compare == "ridopel":
+            z = dict(z, experts=8)          # 8 experts of half the dense inner size each: four times the dense layer's weights
+        configs = {"nufolix": nufolix_configs, "ridopel": ridopel_configs}.get(args.compare, compare_configs)(z)
         for name, cfg in configs.items():
             vocab = z["vocab"]
             lm = blm.load_random(cfg, seed=0, dtype="bfloat16", max_seq_len=4096, max_batch=64, max_tokens=64 * 1024)
@@ -525,7 +654,7 @@ def run_compare(args):
             print(json.dumps(line), flush=True)
             del lm, engine
             torch.cuda.empty_cache()
-        alone = nufolix_kernels(z, pk) if args.compare == "nufolix" else compare_kernels(z, pk)
+        alone = {"nufolix": nufolix_kernels, "ridopel": ridopel_kernels}.get(args.compare, compare_kernels)(z, pk)
         print(json.dumps({"compare": size, "kernels": alone, "peaks": pk["source"]}), flush=True)
     return 0
 
@@ -640,7 +769,7 @@ def main():
     ap.add_argument("--only", default=None, choices=["decode", "prefill", "sweep"],
                     help="run one workload briefly (for profilers), or a sweep over batch sizes and context lengths")
     ap.add_argument("--prompt-tokens", type=int, default=0, help="with --only prefill: one prompt of this many tokens instead of the workload's")
-    ap.add_argument("--compare", default=None, choices=["fobilorn", "nufolix"],
+    ap.add_argument("--compare", default=None, choices=["fobilorn", "nufolix", "ridopel"],
                     help="instead of the workload: the named design beside the dense Llama decoder at equal layer sizes "
                          "(prefill and decode throughput, then its kernels alone), one JSON line each")
     ap.add_argument("--size", default=None, choices=sorted(COMPARE_SIZES), help="with --compare: one of the sizes only")
