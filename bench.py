@@ -496,14 +496,14 @@ def nufolix_kernels(z, pk):
 
 
 def ridopel_configs(z):
-    """(llama, ridopel) of one size.  The new design's layers take turns: attention over a cached latent (Llama's head count,
-    a latent of 4 heads' width, half a head rotated), WKV and HGRN2 with heads of Llama's size, each with `experts` experts of
-    which a token uses `top`, whose inner sizes make Llama's together."""
+    """(llama, ridopel) of one size.  The new design's layers take turns: attention over a cached latent (Llama's head count
+    and head size, half of a head's key lanes rotated, a latent of 4 heads' width), WKV and HGRN2 with heads of Llama's size,
+    each with `experts` experts of which a token uses `top`, whose inner sizes make Llama's together."""
     llama = compare_configs(z)["llama"]
     hd, d, H = z["hd"], z["width"], z["heads"]
     mlp = {"kind": "moe", "router": {"experts": z["experts"], "top": z["top"]}, "expert": {"ff": z["inner"] // z["top"], "limit": 7.0}}
     latent = {"type": "latent_attention", "mlp": mlp,
-              "mixer": {"heads": H, "dim": hd, "rot_dim": hd // 2, "vdim": hd, "kv_rank": 4 * hd, "scale": (1.5 * hd) ** -0.5,
+              "mixer": {"heads": H, "dim": hd // 2, "rot_dim": hd // 2, "vdim": hd, "kv_rank": 4 * hd, "scale": hd ** -0.5,
                         "rot": {"dims": hd // 2, "base": 500000.0}}}
     wkv = {"type": "wkv", "mlp": mlp, "mixer": {"heads": d // hd, "dim": hd}}
     hgrn = {"type": "hgrn2", "mlp": mlp, "mixer": {"heads": d // hd, "dim": hd, "vdim": hd}}
@@ -554,18 +554,36 @@ def ridopel_kernels(z, pk):
         partial = None
         if splits > 1:
             partial = torch.empty(K.latent_attention_scratch_floats(n, H, R, splits), dtype=torch.float32, device=dev)
-        ms_new = _time(lambda: K.latent_attention(q_lat, q_rot, pool, bt, st, mixed, H, R, dr, (1.5 * hd) ** -0.5, n_splits=splits,
+        ms_new = _time(lambda: K.latent_attention(q_lat, q_rot, pool, bt, st, mixed, H, R, dr, hd ** -0.5, n_splits=splits,
                                                   partial=partial), reps=3)
-        return ms_llama, ms_new, total, splits
+        if new < 16:
+            return ms_llama, ms_new, total, splits, None
+        # long portions: every head's keys and values written out for the step, under the dense decoder's kernel
+        dk = hd - dr
+        rows = n_seqs * pages_each * K.PAGE
+        gathered = torch.empty((rows, R + dr), dtype=bf, device=dev)
+        up = torch.randn((H * dk + H * hd, R), dtype=bf, device=dev) * R ** -0.5
+        whole = torch.empty((n_seqs * pages_each, 2, H, K.PAGE, hd), dtype=bf, device=dev)
+        qf = torch.randn((n, H * hd), dtype=bf, device=dev)
 
-    ms_l, ms_n, total, splits = attention_case(1, 2048, 0)
+        def written_out():
+            K.latent_gather(pool, bt, st, gathered, pages_each, R + dr)
+            kv = torch.mm(gathered[:, :R], up.t())
+            K.latent_expand(kv, gathered, whole, H, dk, dr, hd, R)
+            K.attention(qf, qf.shape[1], whole, bt, st.cu_seqlens, st.slot_of_seq, st.start_pos, o, n, n_seqs, new, H, H, hd, hd ** -0.5,
+                        max_kv_len=total)
+        return ms_llama, _time(written_out), total, splits, ms_new
+
+    ms_l, ms_n, total, splits, ms_lat = attention_case(1, 2048, 0)
     pairs = 2048 * 2049 / 2
-    flops_l, flops_n = 4.0 * H * hd * pairs, 2.0 * H * (2 * R + dr) * pairs        # the latent is key and value of every head
-    out["attention_prefill_2048"] = {"llama_ms": round(ms_l, 4), "ridopel_ms": round(ms_n, 4), "key_shares": splits,
+    flops_l = 4.0 * H * hd * pairs
+    flops_n = flops_l + 2.0 * 2048 * R * H * (hd - dr + hd)                        # the same pairs and the heads' keys and values
+    out["attention_prefill_2048"] = {"llama_ms": round(ms_l, 4), "ridopel_ms": round(ms_n, 4),
+                                     "ridopel_on_the_latent_ms": round(ms_lat, 4), "key_shares_on_the_latent": splits,
                                      "llama_gflop": round(flops_l / 1e9, 1), "ridopel_gflop": round(flops_n / 1e9, 1),
                                      "llama_frac_bf16": round(flops_l / (ms_l / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
                                      "ridopel_frac_bf16": round(flops_n / (ms_n / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
-    ms_l, ms_n, total, splits = attention_case(64, 1, 1087)
+    ms_l, ms_n, total, splits, _ = attention_case(64, 1, 1087)
     bytes_l, bytes_n = 64 * G * total * 2 * hd * 2, 64 * total * (R + dr) * 2
     out["attention_decode_b64"] = {"llama_ms": round(ms_l, 4), "ridopel_ms": round(ms_n, 4), "keys_seen": total, "key_shares": splits,
                                    "llama_mb": round(bytes_l / 1e6, 1), "ridopel_mb": round(bytes_n / 1e6, 1),

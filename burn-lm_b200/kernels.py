@@ -135,8 +135,12 @@ _protos = {
     },
     "attention_latent": {
         "blm_latent_prepare": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_float, c_void_p, c_int, c_void_p, c_void_p,
-                               c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                               c_void_p],
+                               c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                               c_int, c_int, c_void_p],
+        "blm_latent_gather": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                              c_void_p],
+        "blm_latent_expand": [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                              c_void_p],
         "blm_latent_attention": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
         "blm_sigmoid_gate": [c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_void_p],
@@ -1276,29 +1280,66 @@ def sigmoid_attention(q, pool, block_table, step, out, n_heads, n_kv, key_dim, v
 # attention over a cached latent
 # ------------------------------------------------------------------------------------------------
 def latent_prepare(q_proj, down, c_weight, eps, freq, rot_dims, q_nope, q_rot, pool, block_table, step, n_heads, key_dim, rot_dim,
-                   rank):
+                   rank, q_full=None):
     """q_proj float32 [N, heads * (key_dim + rot_dim)] (every head's unrotated lanes, then its rotated ones) and down
     float32 [N, rank + rot_dim]: q_nope [heads, N, key_dim] (the cache's dtype) takes the unrotated lanes, q_rot float32
     [N, heads, rot_dim] the rotated ones turned by the token's position (lanes 2i, 2i + 1 by position * freq[i] for the first
     rot_dims lanes; freq float64 [rot_dims / 2]); the first `rank` lanes of `down`, RMS-normed with c_weight, and its last
-    rot_dim lanes, turned likewise, go to the token's place in the paged cache ([pages, PAGE, rank + rot_dim])."""
-    _need_cuda(c_weight, freq, q_nope, q_rot, pool, block_table)
+    rot_dim lanes, turned likewise, go to the token's place in the paged cache ([pages, PAGE, rank + rot_dim]).
+    With `q_full` [N, heads, hd] (the cache's dtype, hd >= key_dim + rot_dim) the query goes there instead, a head's
+    unrotated lanes, its turned ones and zeros side by side, and q_nope and q_rot are not written (they may be None)."""
+    _need_cuda(c_weight, freq, q_nope, q_rot, q_full, pool, block_table)
     _f32(q_proj, down, c_weight, q_rot)
     if not q_proj.is_cuda or not down.is_cuda or q_proj.stride(1) != 1 or down.stride(1) != 1:
         raise KernelError("latent_prepare: q_proj and down are CUDA tensors (column ranges of a wider one will do)")
     n = step.n_tokens
     if tuple(q_proj.shape) != (n, n_heads * (key_dim + rot_dim)) or tuple(down.shape) != (n, rank + rot_dim) or c_weight.numel() != rank:
         raise KernelError("latent_prepare: q_proj [N, heads * (key_dim + rot_dim)], down [N, rank + rot_dim], c_weight [rank]")
-    if q_nope.dtype != pool.dtype or tuple(q_nope.shape) != (n_heads, n, key_dim) or tuple(q_rot.shape) != (n, n_heads, rot_dim):
+    hd_full = 0
+    if q_full is not None:
+        hd_full = q_full.shape[-1]
+        if q_full.dtype != pool.dtype or tuple(q_full.shape) != (n, n_heads, hd_full) or hd_full < key_dim + rot_dim or not q_full.is_contiguous():
+            raise KernelError("latent_prepare: q_full [N, heads, hd >= key_dim + rot_dim] in the cache's dtype")
+    elif (q_nope is None or q_rot is None or q_nope.dtype != pool.dtype or tuple(q_nope.shape) != (n_heads, n, key_dim)
+          or tuple(q_rot.shape) != (n, n_heads, rot_dim)):
         raise KernelError("latent_prepare: q_nope [heads, N, key_dim] in the cache's dtype, q_rot float32 [N, heads, rot_dim]")
     if pool.numel() % (PAGE * (rank + rot_dim)):
         raise KernelError("latent_prepare: the pool does not consist of pages [PAGE, rank + rot_dim]")
     if rot_dims and (freq is None or freq.dtype != torch.float64 or freq.numel() != rot_dims // 2):
         raise KernelError("latent_prepare: freq must be float64 [rot_dims / 2]")
     _call("attention_latent", "blm_latent_prepare", _ptr(q_proj), c_longlong(q_proj.stride(0)), _ptr(down), c_longlong(down.stride(0)),
-          _ptr(c_weight), c_float(eps), _ptr(freq), int(rot_dims), _ptr(q_nope), _ptr(q_rot), _ptr(pool), _code(pool.dtype),
-          _ptr(step.token_seq), _ptr(step.token_pos), _ptr(step.slot_of_seq), _ptr(block_table), block_table.shape[1], n, n_heads,
-          key_dim, rot_dim, rank, PAGE, _stream())
+          _ptr(c_weight), c_float(eps), _ptr(freq), int(rot_dims), _ptr(q_nope), _ptr(q_rot), _ptr(q_full), int(hd_full), _ptr(pool),
+          _code(pool.dtype), _ptr(step.token_seq), _ptr(step.token_pos), _ptr(step.slot_of_seq), _ptr(block_table), block_table.shape[1],
+          n, n_heads, key_dim, rot_dim, rank, PAGE, _stream())
+
+
+def latent_gather(pool, block_table, step, out, pages_each, lanes):
+    """The cached pages of the step's sequences side by side: out [n_seqs * pages_each, PAGE, lanes] takes page p of
+    sequence s at s * pages_each + p; positions a sequence has not reached are zeros."""
+    _need_cuda(pool, block_table, out)
+    if out.dtype != pool.dtype or out.numel() != step.n_seqs * pages_each * PAGE * lanes or not out.is_contiguous():
+        raise KernelError("latent_gather: out [n_seqs * pages_each, PAGE, lanes] in the cache's dtype")
+    if pool.numel() % (PAGE * lanes) or pages_each > block_table.shape[1]:
+        raise KernelError("latent_gather: the pool's pages are [PAGE, lanes]; a sequence has at most the table's pages")
+    _call("attention_latent", "blm_latent_gather", _ptr(pool), _code(pool.dtype), _ptr(block_table), block_table.shape[1],
+          _ptr(step.cu_seqlens), _ptr(step.slot_of_seq), _ptr(step.start_pos), _ptr(out), step.n_seqs, int(pages_each), int(lanes), PAGE,
+          _stream())
+
+
+def latent_expand(kv, gathered, out, n_heads, key_dim, rot_dim, value_dim, rank):
+    """Pages of whole keys and values for the grouped-query attention kernels.  kv [rows, heads * key_dim + heads *
+    value_dim]: every gathered position's unrotated keys of all heads, then its values; gathered [rows, rank + rot_dim]
+    gives the rotated key part all heads share.  out [rows / PAGE, 2, heads, PAGE, hd]: keys [unrotated | rotated | zeros]
+    and values [value | zeros]."""
+    _need_cuda(kv, gathered, out)
+    rows, hd = gathered.shape[0], out.shape[-1]
+    if (kv.dtype != out.dtype or gathered.dtype != out.dtype or kv.stride(1) != 1 or not gathered.is_contiguous() or not out.is_contiguous()
+            or tuple(kv.shape) != (rows, n_heads * (key_dim + value_dim)) or gathered.shape[1] != rank + rot_dim or rows % PAGE
+            or tuple(out.shape) != (rows // PAGE, 2, n_heads, PAGE, hd) or hd < max(key_dim + rot_dim, value_dim)):
+        raise KernelError("latent_expand: kv [rows, heads * (key_dim + value_dim)], gathered [rows, rank + rot_dim], "
+                          "out [rows / PAGE, 2, heads, PAGE, hd]")
+    _call("attention_latent", "blm_latent_expand", _ptr(kv), c_longlong(kv.stride(0)), _ptr(gathered), _ptr(out), _code(out.dtype),
+          rows // PAGE, n_heads, key_dim, rot_dim, value_dim, rank, hd, PAGE, _stream())
 
 
 def latent_attention_scratch_floats(n_tokens, n_heads, rank, n_splits) -> int:

@@ -281,9 +281,11 @@ def _plain_latent(H, dk, dr, dv, R, rot_dims, base, scale, eps, q_proj, down, c_
 
 
 def _latent(dtype, H, dk, dr, dv, R, rot_dims, base, scale, eps, q_proj, down, c_weight, uk, uv, portions, pages=None, splits=1,
-            out_dtype=None):
+            out_dtype=None, expand_from=0):
     """One sequence through prepare, the product with the keys' up-projection, attention over the cached latent and the
-    values' up-projection, in portions; pages: the sequence's pages in the pool, in order."""
+    values' up-projection, in portions; pages: the sequence's pages in the pool, in order.  Portions of `expand_from`
+    tokens or more (when it is not 0) take the other route: whole keys and values of every head, written out for the
+    portion from the gathered latents, under the grouped-query attention kernels."""
     from burn_lm_b200 import kernels as K
     T = q_proj.shape[0]
     n_pages = (T + PAGE - 1) // PAGE
@@ -297,6 +299,23 @@ def _latent(dtype, H, dk, dr, dv, R, rot_dims, base, scale, eps, q_proj, down, c
     outs, at = [], 0
     for k in portions:
         st = step_of((k,), [1], [at])
+        if expand_from and k >= expand_from:
+            hd = 64 if dk + dr <= 64 else 128
+            q = torch.empty((k, H, hd), dtype=dtype, device="cuda")
+            K.latent_prepare(dev(q_proj[at: at + k]), dev(down[at: at + k]), dev(c_weight), eps, freq, rot_dims, None, None, pool, table, st,
+                             H, dk, dr, R, q_full=q)
+            each = (at + k + PAGE - 1) // PAGE
+            gathered = torch.full((each * PAGE, R + dr), float("nan"), dtype=dtype, device="cuda")
+            K.latent_gather(pool, table, st, gathered, each, R + dr)
+            kv = gathered[:, :R] @ torch.cat([dev(uk, dtype), dev(uv, dtype)]).t()
+            whole = torch.full((each, 2, H, PAGE, hd), float("nan"), dtype=dtype, device="cuda")
+            K.latent_expand(kv, gathered, whole, H, dk, dr, dv, R)
+            o = torch.zeros((k, H * hd), dtype=dtype, device="cuda")
+            K.attention(q, H * hd, whole, ints(list(range(each))).view(1, each), st.cu_seqlens, ints([0]), st.start_pos, o, k, 1, k, H, H, hd,
+                        scale, max_kv_len=at + k)
+            outs.append(o.view(k, H, hd)[:, :, :dv].reshape(k, H * dv).float().cpu().numpy())
+            at += k
+            continue
         q_nope = torch.empty((H, k, dk), dtype=dtype, device="cuda")
         q_rot = torch.empty((k, H, dr), dtype=torch.float32, device="cuda")
         K.latent_prepare(dev(q_proj[at: at + k]), dev(down[at: at + k]), dev(c_weight), eps, freq, rot_dims, q_nope, q_rot, pool, table, st,
@@ -332,6 +351,21 @@ def test_latent_attention_in_prompts_portions_and_single_tokens(dtype, H, dk, dr
                                     ((140,) + (1,) * 10, None, 2), ((2,) * 75, [2, 1, 0], 1)):
         got = _latent(dtype, *args, portions, pages=pages, splits=splits)
         assert close(got, want, tol), (portions, splits)
+
+
+@pytest.mark.parametrize("H,dk,dr,rot,dv,R", [s for s in LATENT_SHAPES if s[1] + s[2] <= 128])
+def test_latent_attention_with_the_heads_written_out_for_long_portions(H, dk, dr, rot, dv, R):
+    rng = np.random.default_rng(8)
+    dtype, T, eps, scale, base = torch.bfloat16, 333, 1e-5, 1.7 * (dk + dr) ** -0.5, 300.0
+    q_proj, down = rng.normal(size=(T, H * (dk + dr))), 1.5 * rng.normal(size=(T, R + dr))
+    c_weight, uk, uv = rng.normal(size=R) + 1, rng.normal(size=(H * dk, R)) / np.sqrt(R), rng.normal(size=(H * dv, R)) / np.sqrt(R)
+    args = (H, dk, dr, dv, R, rot, base, scale, eps, q_proj, down, c_weight, uk, uv)
+    rounded = (H, dk, dr, dv, R, rot, base, scale, eps, f32(q_proj), f32(down), f32(c_weight), *(dev(t, dtype).double().cpu().numpy() for t in (uk, uv)))
+    want = _plain_latent(*rounded)
+    for portions, pages in (((333,), None), ((200, 1, 1, 16, 17, 64, 2, 32), [4, 0, 2, 7, 1, 3]), ((64, 64, 128, 77), [5, 4, 3, 2, 1, 0]),
+                            ((130, 3, 200), None)):
+        got = _latent(dtype, *args, portions, pages=pages, expand_from=16)
+        assert close(got, want, 4e-2), portions
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
