@@ -545,8 +545,9 @@ def ridopel_kernels(z, pk):
         ms_llama = _time(lambda: K.attention(q, q.shape[1], pool5, bt, st.cu_seqlens, st.slot_of_seq, st.start_pos, o, n, n_seqs, new,
                                              H, G, hd, hd ** -0.5, window=0, n_splits=1, max_kv_len=total))
         # the key shares the mixer takes at this size (parts.latent_attention.LatentAttention._splits)
-        tiles = (new * H + 15) // 16 * n_seqs
-        splits = max(1, min(-(-2 * K.sm_count() // tiles), total // (2 * K.PAGE), 32))
+        tile = K.latent_attention_tile_rows(bf, H, R, dr, new)
+        tiles = (new * H + tile - 1) // tile * n_seqs
+        splits = max(1, min(2 * K.sm_count() // tiles, total // (2 * K.PAGE), 32))
         pool = torch.randn((n_seqs * pages_each, K.PAGE, R + dr), dtype=bf, device=dev)
         q_lat = torch.randn((H, n, R), dtype=torch.float32, device=dev) * 0.1
         q_rot = torch.randn((n, H, dr), dtype=torch.float32, device=dev)

@@ -280,6 +280,10 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], 
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ void cp_async_16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
 __host__ __device__ inline size_t smem_bytes(int rows, int D) {
     return ((size_t)rows * (D + 8) + (size_t)KC * (D + 8) + (size_t)rows * PS) * sizeof(__nv_bfloat16) + (size_t)2 * rows * SS * sizeof(float);
 }
@@ -316,14 +320,16 @@ __global__ void __launch_bounds__(lat::THREADS, 2)
     __shared__ int page_of[KC];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
     const int* table = block_table + (size_t)slot_of_seq[seq] * table_stride;
-    for (int idx = tid; idx < ROWS * D; idx += THREADS) {
-        const int row = idx / D, d = idx % D;
-        float v = 0.f;
-        if (row < n_rows) {
-            const int r = r0 + row, n = first + r / H, h = r % H;
-            v = d < R ? q_lat[((size_t)h * n_tokens + n) * R + d] : q_rot[((size_t)n * H + h) * dr + (d - R)];
+    for (int row = warp; row < ROWS; row += THREADS / 32) {      // a warp a row: no division an element, loads side by side
+        const int r = r0 + row, n = first + r / H, h = r % H;
+        const float* lat_row = q_lat + ((size_t)h * n_tokens + n) * R;
+        const float* rot_row = q_rot + ((size_t)n * H + h) * dr;
+#pragma unroll 4
+        for (int d = lane; d < D; d += 32) {
+            float v = 0.f;
+            if (row < n_rows) v = d < R ? lat_row[d] : rot_row[d - R];
+            Qs[row * LD + d] = __float2bfloat16(v);
         }
-        Qs[row * LD + d] = __float2bfloat16(v);
     }
     if (tid < ROWS) {
         m_s[tid] = -INFINITY;
@@ -342,12 +348,15 @@ __global__ void __launch_bounds__(lat::THREADS, 2)
         __syncthreads();                     // the chunk before is used up (and Qs, m_s, l_s are written)
         if (tid < KC) page_of[tid] = tid < nk ? table[(k0 + tid) / page_size] : 0;
         __syncthreads();
-        for (int idx = tid; idx < KC * vecs; idx += THREADS) {
-            const int j = idx / vecs, c = idx % vecs;
-            uint4 v = make_uint4(0, 0, 0, 0);              // keys beyond the share are zeros: a weight of 0 silences no NaN
-            if (j < nk) v = *reinterpret_cast<const uint4*>(pool + ((size_t)page_of[j] * page_size + (k0 + j) % page_size) * D + c * 8);
-            *reinterpret_cast<uint4*>(Ks + j * LD + c * 8) = v;
+        for (int idx = tid; idx < KC * vecs; idx += THREADS) {   // asynchronous copies: all of a thread's pieces are on their way at once
+            const int j = idx / vecs, c = idx - j * vecs;
+            __nv_bfloat16* dst = Ks + j * LD + c * 8;
+            if (j < nk)
+                cp_async_16(dst, pool + ((size_t)page_of[j] * page_size + (k0 + j) % page_size) * D + c * 8);
+            else
+                *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);   // keys beyond the share are zeros: a weight of 0 silences no NaN
         }
+        cp_async_wait_all();
         __syncthreads();
         {                                    // scores
             const int nt = warp & 3, half = warp >> 2;

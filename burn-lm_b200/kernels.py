@@ -143,6 +143,7 @@ _protos = {
                               c_void_p],
         "blm_latent_attention": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+        "blm_latent_attention_tile_rows": [c_int, c_int, c_int, c_int, c_int],
         "blm_sigmoid_gate": [c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_void_p],
     },
     "moe": {
@@ -1344,6 +1345,12 @@ def latent_expand(kv, gathered, out, n_heads, key_dim, rot_dim, value_dim, rank)
 
 def latent_attention_scratch_floats(n_tokens, n_heads, rank, n_splits) -> int:
     return n_splits * n_tokens * n_heads * (rank + 2) if n_splits > 1 else 0
+
+
+def latent_attention_tile_rows(dtype, n_heads, rank, rot_dim, max_q_len) -> int:
+    """How many rows (new token x head) a block of latent_attention owns at these sizes: 16 on the CUDA cores, 16 or 32
+    on the tensor cores (a bfloat16 cache whose latent and rotated part are multiples of 16 lanes, up to 512)."""
+    return int(_lib("attention_latent").blm_latent_attention_tile_rows(_code(dtype), n_heads, rank, rot_dim, max_q_len))
 
 
 def latent_attention(q_lat, q_rot, pool, block_table, step, out, n_heads, rank, rot_dim, scale, n_splits=1, partial=None):

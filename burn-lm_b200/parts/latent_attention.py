@@ -105,9 +105,10 @@ class LatentAttention(Part):
         """Over how many blocks a row's keys are cut: a few tokens with many keys leave most multiprocessors idle
         otherwise.  Every block should still have a few pages."""
         s = self.spec
-        tiles = (step.max_q_len * s.n_heads + 15) // 16 * step.n_seqs
+        rows = K.latent_attention_tile_rows(self.runtime.dtype, s.n_heads, s.rank, s.rot_dim, step.max_q_len)
+        tiles = (step.max_q_len * s.n_heads + rows - 1) // rows * step.n_seqs
         want = BLOCKS_PER_SM * K.sm_count(self.runtime.device)
-        return max(1, min((want + tiles - 1) // tiles, step.max_kv_len // (2 * K.PAGE), 32))
+        return max(1, min(want // tiles, step.max_kv_len // (2 * K.PAGE), 32))     # no block left over for a second round
 
     def forward(self, x, step, cache):
         s, rt = self.spec, self.runtime

@@ -368,12 +368,13 @@ def test_latent_attention_with_the_heads_written_out_for_long_portions(H, dk, dr
         assert close(got, want, 4e-2), portions
 
 
+@pytest.mark.parametrize("dr,R", [(4, 16), (16, 32)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_one_key_far_back_at_page_borders_and_the_diagonal(dtype):
+def test_one_key_far_back_at_page_borders_and_the_diagonal(dtype, dr, R):
     """All scores are zero but one pair's, planted in a rotated lane that does not turn: the query's output is that
     position's value if it may see it, and the mean of what it sees otherwise.  The key sits at the sequence's start, on
     both sides of page borders, on the diagonal, and one position after the query."""
-    H, dk, dr, dv, R, T = 2, 8, 4, 8, 16, 400
+    H, dk, dv, T = 2, 8, 8, 400
     rng = np.random.default_rng(7)
     c_weight, uk, uv = np.ones(R), rng.normal(size=(H * dk, R)), rng.normal(size=(H * dv, R))
     for key_at in (0, 63, 64, 127, 128, 255, 256, 320, 398, 399):
@@ -671,10 +672,28 @@ def test_the_trace_runner_as_a_child_process(tmp_path):
         assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == [f"done {s['step']}" for s in steps]
         wa, wb = P.forward(cfg, tensors, a), P.forward(cfg, tensors, b)
         read = lambda n: np.fromfile(out / f"{n}.f32", dtype="<f4").reshape(-1, cfg["vocab"])
-        errs = list(row_error(read(0), np.stack([wa[0], wa[69], wb[4]]))) + list(row_error(read(1), wb[5][None]))
-        for t in range(4):
-            rows = [wa[71 + t]] + ([wb[6 + t]] if t < 3 else [])
-            errs += list(row_error(read(2 + t), np.stack(rows)))
+        want = {0: [wa[0], wa[69], wb[4]], 1: [wb[5]]}
+        want.update({2 + t: [wa[71 + t]] + ([wb[6 + t]] if t < 3 else []) for t in range(4)})
+        if dtype == "bfloat16":
+            # the runner adds no arithmetic: the same steps through an engine in this process give the same rows, up to what
+            # another choice of kernels for another cache size rounds differently (the short request's second token is a
+            # close call between two experts in bfloat16, so the plain rows judge float32 and the long request only)
+            from burn_lm_b200 import StepEntry
+            engine = engine_for(folder, dtype, max_tokens=256)
+            slot = {}
+            for s in steps:
+                for e in s["entries"]:
+                    if e["id"] not in slot:
+                        slot[e["id"]] = engine.acquire()
+                rows = engine.step([StepEntry(slot[e["id"]], e["tokens"], e["want"]) for e in s["entries"]])
+                if any(e["want"] for e in s["entries"]):
+                    assert row_error(read(s["step"]), rows.cpu().numpy().astype(np.float64)).max() < tol / 2, s["step"]
+                for name in s["end"]:
+                    engine.release(slot.pop(name))
+            a_rows = [row_error(read(n)[:1], np.stack(w[:1]))[0] for n, w in want.items() if n != 1]
+            assert rows_ok(a_rows, dtype, tol), a_rows
+            continue
+        errs = [e for n, w in want.items() for e in row_error(read(n), np.stack(w))]
         assert len(errs) == 11 and rows_ok(errs, dtype, tol), errs
 
 
