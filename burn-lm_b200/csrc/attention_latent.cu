@@ -7,7 +7,9 @@
 //
 //   blm_latent_prepare    q projection -> q_nope [H][N][dk] (the batched product's operand) and rotated q_rot [N][H][dr];
 //                         down projection -> RMS-normed c and rotated k_rot, appended to the token's place in the cache
-//   blm_latent_attention  causal softmax attention of a step's rows over the cache, keys cut over `splits` blocks
+//   blm_latent_attention  causal softmax attention of a step's rows over the cache, keys cut over `splits` blocks; options:
+//                         a window (position i sees j with 0 <= i - j < window) and a sink per head (one more entry
+//                         exp(sink_h) in the softmax's denominator, without a key or a value, not scaled)
 //   blm_latent_gather     the pages of a step's sequences, copied side by side in the order of the sequences
 //   blm_latent_expand     keys and values of every head, made from gathered latents, laid out as pages of the
 //                         grouped-query attention kernels ([2][heads][page_size][hd]): long prompts run those
@@ -18,15 +20,18 @@
 
 BLM_API const char* blm_attention_latent_last_error() { return g_blm_error; }
 
-// lanes 2i and 2i + 1 of a rotated part turn by pos * freq[i]; lanes from rot_dims on pass unchanged.  The angle, its sine
-// and cosine are taken in fp64 and applied in fp32.
-__device__ __forceinline__ float rotated_lane(const float* src, int j, int rot_dims, int pos, const double* __restrict__ freq) {
+// lanes 2i and 2i + 1 of a rotated part (`halves`: lanes i and i + rot_dims / 2) turn by pos * freq[i]; lanes from rot_dims
+// on pass unchanged.  The angle, its sine and cosine are taken in fp64 and applied in fp32.
+__device__ __forceinline__ float rotated_lane(const float* src, int j, int rot_dims, int pos, const double* __restrict__ freq,
+                                              int halves) {
     if (j >= rot_dims) return src[j];
-    const int i = j >> 1;
+    const int half = rot_dims >> 1;
+    const int i = halves ? (j < half ? j : j - half) : (j >> 1);
+    const int ia = halves ? i : 2 * i, ib = halves ? i + half : 2 * i + 1;
     double s, c;
     sincos((double)pos * freq[i], &s, &c);
-    const float a = src[2 * i], b = src[2 * i + 1], cf = (float)c, sf = (float)s;
-    return (j & 1) ? b * cf + a * sf : a * cf - b * sf;
+    const float a = src[ia], b = src[ib], cf = (float)c, sf = (float)s;
+    return j == ib ? b * cf + a * sf : a * cf - b * sf;
 }
 
 template <typename T>
@@ -37,7 +42,7 @@ __global__ void latent_prepare_kernel(const float* __restrict__ qp, long long qp
                                       const int* __restrict__ token_seq,
                                       const int* __restrict__ token_pos, const int* __restrict__ slot_of_seq,
                                       const int* __restrict__ block_table, int table_stride, int n_tokens, int H, int dk, int dr,
-                                      int R, int page_size) {
+                                      int R, int page_size, int halves) {
     __shared__ float red[33];
     const int n = blockIdx.x;
     const int seq = token_seq[n];
@@ -49,7 +54,7 @@ __global__ void latent_prepare_kernel(const float* __restrict__ qp, long long qp
             const int h = idx / hd_full, d = idx % hd_full;
             float v = 0.f;
             if (real && d < dk) v = qrow[(size_t)h * (dk + dr) + d];
-            else if (real && d < dk + dr) v = rotated_lane(qrow + (size_t)h * (dk + dr) + dk, d - dk, rot_dims, pos, freq);
+            else if (real && d < dk + dr) v = rotated_lane(qrow + (size_t)h * (dk + dr) + dk, d - dk, rot_dims, pos, freq, halves);
             q_full[((size_t)n * H + h) * hd_full + d] = from_f32<T>(v);
         }
     }
@@ -59,7 +64,7 @@ __global__ void latent_prepare_kernel(const float* __restrict__ qp, long long qp
     }
     for (int idx = threadIdx.x; q_full == nullptr && idx < H * dr; idx += blockDim.x) {
         const int h = idx / dr, j = idx % dr;
-        q_rot[((size_t)n * H + h) * dr + j] = real ? rotated_lane(qrow + (size_t)h * (dk + dr) + dk, j, rot_dims, pos, freq) : 0.f;
+        q_rot[((size_t)n * H + h) * dr + j] = real ? rotated_lane(qrow + (size_t)h * (dk + dr) + dk, j, rot_dims, pos, freq, halves) : 0.f;
     }
     if (!real) return;
     const float* row = dkv + (size_t)n * dkv_stride;
@@ -70,14 +75,16 @@ __global__ void latent_prepare_kernel(const float* __restrict__ qp, long long qp
     const int page = block_table[(size_t)slot_of_seq[seq] * table_stride + pos / page_size];
     T* dst = pool + ((size_t)page * page_size + pos % page_size) * (R + dr);
     for (int r = threadIdx.x; r < R; r += blockDim.x) dst[r] = from_f32<T>(row[r] * inv * c_weight[r]);
-    for (int j = threadIdx.x; j < dr; j += blockDim.x) dst[R + j] = from_f32<T>(rotated_lane(row + R, j, rot_dims, pos, freq));
+    for (int j = threadIdx.x; j < dr; j += blockDim.x) dst[R + j] = from_f32<T>(rotated_lane(row + R, j, rot_dims, pos, freq, halves));
 }
 
 BLM_API int blm_latent_prepare(const float* qp, long long qp_stride, const float* dkv, long long dkv_stride, const float* c_weight,
                                float eps, const double* freq, int rot_dims, void* q_nope, float* q_rot, void* q_full, int hd_full,
                                void* pool, int dtype,
                                const int* token_seq, const int* token_pos, const int* slot_of_seq, const int* block_table,
-                               int table_stride, int n_tokens, int H, int dk, int dr, int R, int page_size, cudaStream_t stream) {
+                               int table_stride, int n_tokens, int H, int dk, int dr, int R, int page_size, int halves,
+                               cudaStream_t stream) {
+    // halves 0: the turning lanes are paired (2i, 2i + 1); 1: (i, i + rot_dims / 2)
     if (n_tokens == 0) return BLM_OK;
     BLM_REQUIRE(H > 0 && dk > 0 && dr >= 0 && R > 0 && page_size > 0, "latent_prepare: bad sizes");
     BLM_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= dr, "latent_prepare: %d rotated lanes of %d", rot_dims, dr);
@@ -87,12 +94,12 @@ BLM_API int blm_latent_prepare(const float* qp, long long qp_stride, const float
         latent_prepare_kernel<float><<<n_tokens, 256, 0, stream>>>(qp, qp_stride, dkv, dkv_stride, c_weight, eps, freq, rot_dims,
                                                                    (float*)q_nope, q_rot, (float*)q_full, hd_full, (float*)pool, token_seq, token_pos,
                                                                    slot_of_seq, block_table, table_stride, n_tokens, H, dk, dr, R,
-                                                                   page_size);
+                                                                   page_size, halves);
     else if (dtype == BLM_BF16)
         latent_prepare_kernel<__nv_bfloat16><<<n_tokens, 256, 0, stream>>>(qp, qp_stride, dkv, dkv_stride, c_weight, eps, freq, rot_dims,
                                                                            (__nv_bfloat16*)q_nope, q_rot, (__nv_bfloat16*)q_full, hd_full, (__nv_bfloat16*)pool,
                                                                            token_seq, token_pos, slot_of_seq, block_table,
-                                                                           table_stride, n_tokens, H, dk, dr, R, page_size);
+                                                                           table_stride, n_tokens, H, dk, dr, R, page_size, halves);
     else
         return blm_fail(BLM_BAD_ARGUMENT, "latent_prepare: dtype %d", dtype);
     return blm_check_launch("latent_prepare");
@@ -111,7 +118,7 @@ __global__ void __launch_bounds__(kLatThreads)
                             const int* __restrict__ block_table, int table_stride, const int* __restrict__ cu_seqlens,
                             const int* __restrict__ slot_of_seq, const int* __restrict__ start_pos, TO* __restrict__ out,
                             float* __restrict__ partial, int n_tokens, int H, int R, int dr, int page_size, float scale,
-                            int n_splits) {
+                            int n_splits, int window, const float* __restrict__ sink) {
     const int seq = blockIdx.y, split = blockIdx.z;
     const int first = cu_seqlens[seq];
     const int n_new = cu_seqlens[seq + 1] - first;
@@ -121,9 +128,12 @@ __global__ void __launch_bounds__(kLatThreads)
     const int n_rows = min(kTM, rows_total - r0);
     const int start = start_pos[seq];
     const int kv_end = start + (r0 + n_rows - 1) / H + 1;          // keys the tile's last row sees
-    const int pages_total = (kv_end + page_size - 1) / page_size;
+    // the tile's first row sees no key before its window: the walk starts at that key's page (window 0: at the first page)
+    const int page_lo = window > 0 ? max(0, start + r0 / H - window + 1) / page_size : 0;
+    const int pages_total = (kv_end + page_size - 1) / page_size - page_lo;
     const int pages_per = (pages_total + n_splits - 1) / n_splits;
-    const int key_lo = min(kv_end, split * pages_per * page_size), key_hi = min(kv_end, (split + 1) * pages_per * page_size);
+    const int key_lo = min(kv_end, (page_lo + split * pages_per) * page_size);
+    const int key_hi = min(kv_end, (page_lo + (split + 1) * pages_per) * page_size);
     const int D = R + dr, KS = D + 1;
     extern __shared__ __align__(16) float lat_smem[];
     float* Pt = lat_smem;                    // [kKC][kTM]: a chunk's weights, key by key
@@ -143,9 +153,10 @@ __global__ void __launch_bounds__(kLatThreads)
         }
         Qs[idx] = v;
     }
-    if (tid < kTM) {
-        m_s[tid] = -INFINITY;
-        l_s[tid] = 0.f;
+    if (tid < kTM) {                         // the sink is one more entry of the first share: a score without a value
+        const bool with_sink = sink != nullptr && split == 0;
+        m_s[tid] = with_sink ? sink[(r0 + tid) % H] : -INFINITY;
+        l_s[tid] = with_sink ? 1.f : 0.f;
     }
     float acc[kTM][CPT];
 #pragma unroll
@@ -176,9 +187,10 @@ __global__ void __launch_bounds__(kLatThreads)
                 sb = fmaf(qv, kb[d], sb);
             }
             const int limit = start + (r0 + row) / H;            // the row's own position
+            const int from = window > 0 ? limit - window + 1 : 0; // the first key it sees
             const bool live = row < n_rows;
-            Ss[row * kKC + jp] = (live && jp < nk && k0 + jp <= limit) ? sa * scale : -INFINITY;
-            Ss[row * kKC + jp + 16] = (live && jp + 16 < nk && k0 + jp + 16 <= limit) ? sb * scale : -INFINITY;
+            Ss[row * kKC + jp] = (live && jp < nk && k0 + jp <= limit && k0 + jp >= from) ? sa * scale : -INFINITY;
+            Ss[row * kKC + jp + 16] = (live && jp + 16 < nk && k0 + jp + 16 <= limit && k0 + jp + 16 >= from) ? sb * scale : -INFINITY;
         }
         __syncthreads();
 #pragma unroll
@@ -295,7 +307,7 @@ __global__ void __launch_bounds__(lat::THREADS, 2)
                                 const int* __restrict__ block_table, int table_stride, const int* __restrict__ cu_seqlens,
                                 const int* __restrict__ slot_of_seq, const int* __restrict__ start_pos, TO* __restrict__ out,
                                 float* __restrict__ partial, int n_tokens, int H, int R, int dr, int page_size, float scale,
-                                int n_splits) {
+                                int n_splits, int window, const float* __restrict__ sink) {
     using namespace lat;
     constexpr int ROWS = 16 * MT;
     const int seq = blockIdx.y, split = blockIdx.z;
@@ -307,9 +319,11 @@ __global__ void __launch_bounds__(lat::THREADS, 2)
     const int n_rows = min(ROWS, rows_total - r0);
     const int start = start_pos[seq];
     const int kv_end = start + (r0 + n_rows - 1) / H + 1;          // keys the tile's last row sees
-    const int pages_total = (kv_end + page_size - 1) / page_size;
+    const int page_lo = window > 0 ? max(0, start + r0 / H - window + 1) / page_size : 0;   // as in the kernel above
+    const int pages_total = (kv_end + page_size - 1) / page_size - page_lo;
     const int pages_per = (pages_total + n_splits - 1) / n_splits;
-    const int key_lo = min(kv_end, split * pages_per * page_size), key_hi = min(kv_end, (split + 1) * pages_per * page_size);
+    const int key_lo = min(kv_end, (page_lo + split * pages_per) * page_size);
+    const int key_hi = min(kv_end, (page_lo + (split + 1) * pages_per) * page_size);
     const int D = R + dr, LD = D + 8;
     extern __shared__ __align__(16) unsigned char lat_mma_smem[];
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(lat_mma_smem);      // [ROWS][LD]
@@ -332,8 +346,9 @@ __global__ void __launch_bounds__(lat::THREADS, 2)
         }
     }
     if (tid < ROWS) {
-        m_s[tid] = -INFINITY;
-        l_s[tid] = 0.f;
+        const bool with_sink = sink != nullptr && split == 0;
+        m_s[tid] = with_sink ? sink[(r0 + tid) % H] : -INFINITY;
+        l_s[tid] = with_sink ? 1.f : 0.f;
     }
     float acc[MT][NT][4];
 #pragma unroll
@@ -385,7 +400,8 @@ __global__ void __launch_bounds__(lat::THREADS, 2)
 #pragma unroll
         for (int rr = 0; rr < 2 * MT; ++rr) {     // running softmax: a warp takes 2 MT rows, a lane a key
             const int row = 2 * MT * warp + rr;
-            const bool seen = row < n_rows && lane < nk && k0 + lane <= start + (r0 + row) / H;
+            const int limit = start + (r0 + row) / H;
+            const bool seen = row < n_rows && lane < nk && k0 + lane <= limit && (window <= 0 || k0 + lane > limit - window);
             const float s = seen ? (Ss[row * SS + lane] + Ss[(ROWS + row) * SS + lane]) * scale : -INFINITY;
             const float m_old = m_s[row];
             const float m_new = fmaxf(m_old, warp_max(s));
@@ -510,12 +526,14 @@ BLM_API long long blm_latent_attention_scratch_floats(int n_tokens, int H, int R
 BLM_API int blm_latent_attention(const float* q_lat, const float* q_rot, const void* pool, int dtype, const int* block_table,
                                  int table_stride, const int* cu_seqlens, const int* slot_of_seq, const int* start_pos,
                                  const int* token_seq, void* out, int out_dtype, float* partial, int n_tokens, int n_seqs,
-                                 int max_q_len, int H, int R, int dr, int page_size, float scale, int n_splits,
-                                 cudaStream_t stream) {
+                                 int max_q_len, int H, int R, int dr, int page_size, float scale, int n_splits, int window,
+                                 const float* sink, cudaStream_t stream) {
+    // window: 0 for every earlier key; sink: float32 [H] or null
     if (n_tokens == 0 || n_seqs == 0) return BLM_OK;
     BLM_REQUIRE(H > 0 && R > 0 && dr >= 0 && page_size > 0 && max_q_len > 0 && n_splits >= 1, "latent_attention: bad sizes");
     BLM_REQUIRE(R <= 4 * kLatThreads, "latent_attention: a latent of %d lanes; this kernel takes up to %d", R, 4 * kLatThreads);
     BLM_REQUIRE(n_splits == 1 || partial != nullptr, "latent_attention: key shares need their scratch");
+    BLM_REQUIRE(window >= 0, "latent_attention: a window of %d", window);
     const int D = R + dr;
     if (latent_takes_mma(dtype, R, dr) && (out_dtype == BLM_BF16 || out_dtype == BLM_F32) && ((size_t)pool & 15) == 0) {
         const int rows = blm_latent_attention_tile_rows(dtype, H, R, dr, max_q_len);
@@ -533,7 +551,7 @@ BLM_API int blm_latent_attention(const float* q_lat, const float* q_rot, const v
         }                                                                                                                \
         kern<<<grid, lat::THREADS, smem, stream>>>(q_lat, q_rot, (const __nv_bfloat16*)pool, block_table, table_stride,  \
                                                    cu_seqlens, slot_of_seq, start_pos, (TO*)out, partial, n_tokens, H,   \
-                                                   R, dr, page_size, scale, n_splits);                                   \
+                                                   R, dr, page_size, scale, n_splits, window, sink);                     \
     }
 #define BLM_LAT_MMA_N(TO, MT)                                            \
     if (nt == 2) BLM_LAT_MMA(TO, MT, 2)                                  \
@@ -570,7 +588,7 @@ BLM_API int blm_latent_attention(const float* q_lat, const float* q_rot, const v
         }                                                                                                                \
         kern<<<grid, kLatThreads, smem, stream>>>(q_lat, q_rot, (const T*)pool, block_table, table_stride, cu_seqlens,   \
                                                   slot_of_seq, start_pos, (TO*)out, partial, n_tokens, H, R, dr,         \
-                                                  page_size, scale, n_splits);                                           \
+                                                  page_size, scale, n_splits, window, sink);                             \
     }
 #define BLM_LAT_C(T, TO)                                                 \
     if (cpt == 1) BLM_LAT(T, TO, 1)                                      \
@@ -603,10 +621,13 @@ BLM_API int blm_latent_attention(const float* q_lat, const float* q_rot, const v
 template <typename T>
 __global__ void latent_gather_kernel(const T* __restrict__ pool, const int* __restrict__ block_table, int table_stride,
                                      const int* __restrict__ cu_seqlens, const int* __restrict__ slot_of_seq,
-                                     const int* __restrict__ start_pos, T* __restrict__ out, int pages_each, int D, int page_size) {
+                                     const int* __restrict__ start_pos, T* __restrict__ out, int pages_each, int D, int page_size,
+                                     int window) {
     const int p = blockIdx.x, seq = blockIdx.y;
     const int kv_len = start_pos[seq] + cu_seqlens[seq + 1] - cu_seqlens[seq];
-    const int live = min(page_size, kv_len - p * page_size);
+    // pages that lie wholly before the window of the step's first token may have been given back: zeros for them
+    const bool before = window > 0 && (p + 1) * page_size <= start_pos[seq] - window + 1;
+    const int live = before ? 0 : min(page_size, kv_len - p * page_size);
     T* dst = out + ((size_t)seq * pages_each + p) * page_size * D;
     const T* src = live > 0 ? pool + (size_t)block_table[(size_t)slot_of_seq[seq] * table_stride + p] * page_size * D : nullptr;
     const int n_live = live > 0 ? live * D : 0, n_all = page_size * D;
@@ -622,7 +643,8 @@ __global__ void latent_gather_kernel(const T* __restrict__ pool, const int* __re
 
 BLM_API int blm_latent_gather(const void* pool, int dtype, const int* block_table, int table_stride, const int* cu_seqlens,
                               const int* slot_of_seq, const int* start_pos, void* out, int n_seqs, int pages_each, int D,
-                              int page_size, cudaStream_t stream) {
+                              int page_size, int window, cudaStream_t stream) {
+    // window: 0, or the mixer's window: pages wholly before it are not read
     if (n_seqs == 0 || pages_each == 0) return BLM_OK;
     BLM_REQUIRE(n_seqs > 0 && n_seqs <= 65535 && pages_each > 0 && D > 0 && page_size > 0, "latent_gather: bad sizes");
     BLM_REQUIRE(pages_each <= table_stride, "latent_gather: %d pages a sequence, the table has %d", pages_each, table_stride);
@@ -630,10 +652,10 @@ BLM_API int blm_latent_gather(const void* pool, int dtype, const int* block_tabl
     const dim3 grid(pages_each, n_seqs);
     if (dtype == BLM_BF16)
         latent_gather_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)pool, block_table, table_stride, cu_seqlens,
-                                                                     slot_of_seq, start_pos, (__nv_bfloat16*)out, pages_each, D, page_size);
+                                                                     slot_of_seq, start_pos, (__nv_bfloat16*)out, pages_each, D, page_size, window);
     else if (dtype == BLM_F32)
         latent_gather_kernel<float><<<grid, 256, 0, stream>>>((const float*)pool, block_table, table_stride, cu_seqlens, slot_of_seq,
-                                                             start_pos, (float*)out, pages_each, D, page_size);
+                                                             start_pos, (float*)out, pages_each, D, page_size, window);
     else
         return blm_fail(BLM_BAD_ARGUMENT, "latent_gather: dtype %d", dtype);
     return blm_check_launch("latent_gather");
@@ -678,32 +700,33 @@ BLM_API int blm_latent_expand(const void* kv, long long ld, const void* gathered
 }
 
 // ---------------------------------------------------------------------------------------------
-// out = o * sigmoid(g), element by element: o, out [N][C]; g [N][g_stride] in float32 or the activations' dtype
+// out = o * sigmoid(g): o, out [N][C]; g [N][g_stride] in float32 or the activations' dtype, a number for every `share`
+// neighbouring columns of o (1: element by element; a head's value size: a gate per head)
 // ---------------------------------------------------------------------------------------------
 template <typename T, typename TG>
 __global__ void sigmoid_gate_kernel(const T* __restrict__ o, const TG* __restrict__ g, long long g_stride, T* __restrict__ out,
-                                    int cols) {
+                                    int cols, int share) {
     const int n = blockIdx.y;
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= cols) return;
     const size_t i = (size_t)n * cols + c;
-    out[i] = from_f32<T>(to_f32(o[i]) / (1.0f + expf(-to_f32(g[(size_t)n * g_stride + c]))));
+    out[i] = from_f32<T>(to_f32(o[i]) / (1.0f + expf(-to_f32(g[(size_t)n * g_stride + c / share]))));
 }
 
 BLM_API int blm_sigmoid_gate(const void* o, int dtype, const void* g, int g_dtype, long long g_stride, void* out, int rows, int cols,
-                             cudaStream_t stream) {
+                             int share, cudaStream_t stream) {
     if (rows == 0 || cols == 0) return BLM_OK;
-    BLM_REQUIRE(rows > 0 && rows <= 65535 && cols > 0, "sigmoid_gate: bad sizes");
+    BLM_REQUIRE(rows > 0 && rows <= 65535 && cols > 0 && share > 0, "sigmoid_gate: bad sizes");
     const int threads = 256;
     const dim3 grid((cols + threads - 1) / threads, rows);
     if (dtype == BLM_F32 && g_dtype == BLM_F32)
-        sigmoid_gate_kernel<float, float><<<grid, threads, 0, stream>>>((const float*)o, (const float*)g, g_stride, (float*)out, cols);
+        sigmoid_gate_kernel<float, float><<<grid, threads, 0, stream>>>((const float*)o, (const float*)g, g_stride, (float*)out, cols, share);
     else if (dtype == BLM_BF16 && g_dtype == BLM_F32)
         sigmoid_gate_kernel<__nv_bfloat16, float><<<grid, threads, 0, stream>>>((const __nv_bfloat16*)o, (const float*)g, g_stride,
-                                                                                (__nv_bfloat16*)out, cols);
+                                                                                (__nv_bfloat16*)out, cols, share);
     else if (dtype == BLM_BF16 && g_dtype == BLM_BF16)
         sigmoid_gate_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, threads, 0, stream>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)g,
-                                                                                        g_stride, (__nv_bfloat16*)out, cols);
+                                                                                        g_stride, (__nv_bfloat16*)out, cols, share);
     else
         return blm_fail(BLM_BAD_ARGUMENT, "sigmoid_gate: dtypes %d/%d", dtype, g_dtype);
     return blm_check_launch("sigmoid_gate");

@@ -5,6 +5,8 @@
 //   p_j = exp(s_j) / (sink + sum_visible exp(s_j)),  s_j = scale q.k_j      (sink = 1: one more entry of score 0
 //                                                                             that carries no value; 0: plain softmax)
 //   out[n, h] = gate(n, h) * sum_j p_j v_j,  gate = sigmoid(g[n, h]) or 1
+// Options of the scores (ScoreOpts): a number per query head that multiplies its scores, s_j = scale t_h q.k_j; a cap,
+// s_j <- cap tanh(s_j / cap); and a score z_h of the sink other than 0, p_j = exp(s_j) / (exp(z_h) + sum exp(s_j)).
 //
 // The cache page of this family holds the keys [n_kv, page, dk] followed by the values [n_kv, page, dv].
 // Scores, softmax and sums are fp32; q, keys and values are read in the cache's dtype.
@@ -136,13 +138,116 @@ __device__ __forceinline__ void stage_row<__nv_bfloat16>(float* dst, const __nv_
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// After the fused projection [q | k | v | ...] (fp32 rows), head by head:
+//   q_h <- q_h / rms(q_h) * wq   (wq [dk], the same for every head; null: as it is), k_h likewise with wk;
+//   the first rot_dims lanes of q_h and k_h turn by pos * freq[i]: lanes (2i, 2i + 1) when `halves` is 0, lanes
+//   (i, i + rot_dims / 2) when it is 1; the other lanes pass;
+//   v_h <- v_h / rms(v_h) when `value_norm` (no weight);
+// q goes to q_out, k and v to the token's place in the paged cache.  rms(x) = sqrt(mean(x^2) + eps).  A warp a head;
+// the angle, its sine and cosine in fp64, everything else fp32.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float turned_lane(const float* src, const float* w, float inv, int j, int rot_dims, int halves, int pos,
+                                             const double* __restrict__ freq) {
+    if (j >= rot_dims) return src[j] * inv * (w ? w[j] : 1.f);
+    const int half = rot_dims >> 1;
+    const int i = halves ? (j < half ? j : j - half) : (j >> 1);
+    const int ia = halves ? i : 2 * i, ib = halves ? i + half : 2 * i + 1;
+    double sn, cs;
+    sincos((double)pos * freq[i], &sn, &cs);
+    const float a = src[ia] * inv * (w ? w[ia] : 1.f), b = src[ib] * inv * (w ? w[ib] : 1.f), cf = (float)cs, sf = (float)sn;
+    return j == ib ? b * cf + a * sf : a * cf - b * sf;
+}
+
+template <typename T>
+__global__ void head_norm_rope_append_kernel(const float* __restrict__ proj, long long proj_stride, int n_heads, int n_kv, int dk,
+                                             int dv, const float* __restrict__ wq, const float* __restrict__ wk, float eps,
+                                             int value_norm, const double* __restrict__ freq, int rot_dims, int halves,
+                                             T* __restrict__ q_out, T* __restrict__ pool, long long page_elems, int page_size,
+                                             const int* __restrict__ token_seq, const int* __restrict__ token_pos,
+                                             const int* __restrict__ slot_of_seq, const int* __restrict__ block_table,
+                                             int table_stride) {
+    const int n = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const float* p = proj + (size_t)n * proj_stride;
+    const int seq = token_seq[n];
+    const bool real = seq >= 0;                        // a row of no sequence leaves zeros in q and reaches no cache
+    const int pos = real ? token_pos[n] : 0;
+    T* kpage = nullptr;
+    T* vpage = nullptr;
+    int r = 0;
+    if (real) {
+        const int page = block_table[(size_t)slot_of_seq[seq] * table_stride + pos / page_size];
+        r = pos % page_size;
+        kpage = pool + (size_t)page * page_elems;
+        vpage = kpage + (size_t)n_kv * page_size * dk;
+    }
+    const int n_vectors = n_heads + 2 * n_kv;          // the heads of q, then of k, then of v
+    for (int item = warp; item < n_vectors; item += n_warps) {
+        const bool is_q = item < n_heads, is_k = !is_q && item < n_heads + n_kv;
+        const int head = is_q ? item : (is_k ? item - n_heads : item - n_heads - n_kv);
+        const int width = (is_q || is_k) ? dk : dv;
+        const float* src = p + (is_q ? (size_t)head * dk : (is_k ? (size_t)n_heads * dk + (size_t)head * dk
+                                                                  : (size_t)(n_heads + n_kv) * dk + (size_t)head * dv));
+        const float* w = is_q ? wq : (is_k ? wk : nullptr);
+        float inv = 1.f;
+        if (w != nullptr || (!is_q && !is_k && value_norm)) {
+            float ss = 0.f;
+            for (int d = lane; d < width; d += 32) ss += src[d] * src[d];
+            ss = warp_sum(ss);
+            inv = 1.0f / sqrtf(ss / (float)width + eps);
+        }
+        if (is_q) {
+            T* dst = q_out + ((size_t)n * n_heads + head) * dk;
+            for (int d = lane; d < dk; d += 32) dst[d] = from_f32<T>(real ? turned_lane(src, w, inv, d, rot_dims, halves, pos, freq) : 0.f);
+        } else if (is_k) {
+            if (!real) continue;
+            T* dst = kpage + ((size_t)head * page_size + r) * dk;
+            for (int d = lane; d < dk; d += 32) dst[d] = from_f32<T>(turned_lane(src, w, inv, d, rot_dims, halves, pos, freq));
+        } else {
+            if (!real) continue;
+            T* dst = vpage + ((size_t)head * page_size + r) * dv;
+            for (int d = lane; d < dv; d += 32) dst[d] = from_f32<T>(src[d] * inv);
+        }
+    }
+}
+
+BLM_API int blm_head_norm_rope_append(const float* proj, long long proj_stride, int n_tokens, int n_heads, int n_kv, int dk, int dv,
+                                      const float* wq, const float* wk, float eps, int value_norm, const double* freq, int rot_dims,
+                                      int halves, void* q_out, void* pool, int dtype, long long page_elems, int page_size,
+                                      const int* token_seq, const int* token_pos, const int* slot_of_seq, const int* block_table,
+                                      int table_stride, cudaStream_t stream) {
+    if (n_tokens == 0) return BLM_OK;
+    BLM_REQUIRE(n_tokens > 0 && n_heads > 0 && n_kv > 0 && dk > 0 && dv > 0 && page_size > 0, "head_norm_rope_append: bad sizes");
+    BLM_REQUIRE(page_elems == (long long)n_kv * page_size * (dk + dv), "head_norm_rope_append: a page holds n_kv * page * (dk + dv) elements");
+    BLM_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= dk && (rot_dims == 0 || freq != nullptr),
+                "head_norm_rope_append: %d turning lanes of %d", rot_dims, dk);
+    const int vectors = n_heads + 2 * n_kv;
+    const int threads = vectors >= 8 ? 256 : 32 * vectors;
+#define BLM_HNRA(T)                                                                                                              \
+    head_norm_rope_append_kernel<T><<<n_tokens, threads, 0, stream>>>(proj, proj_stride, n_heads, n_kv, dk, dv, wq, wk, eps, value_norm, \
+        freq, rot_dims, halves, (T*)q_out, (T*)pool, page_elems, page_size, token_seq, token_pos, slot_of_seq, block_table, table_stride)
+    if (dtype == BLM_F32) BLM_HNRA(float);
+    else if (dtype == BLM_BF16) BLM_HNRA(__nv_bfloat16);
+    else return blm_fail(BLM_BAD_ARGUMENT, "head_norm_rope_append: dtype %d", dtype);
+#undef BLM_HNRA
+    return blm_check_launch("head_norm_rope_append");
+}
+
+// What a score goes through before the softmax, and what the sink weighs (all optional: null, null, 0).
+struct ScoreOpts {
+    const float* head_scale;     // [n_heads]: multiplies the head's scores beside `scale`
+    const float* sink_logit;     // [n_heads]: the sink's score (null: 0); read only when the softmax has a sink
+    float cap;                   // > 0: s <- cap tanh(s / cap)
+};
+__device__ __forceinline__ float capped(float s, float cap) { return cap > 0.f ? cap * tanhf(s / cap) : s; }
+
 template <typename T>
 __global__ void attention_sink_rows_kernel(const T* __restrict__ q, const T* __restrict__ pool, long long page_elems,
                                            const int* __restrict__ block_table, int table_stride, const int* __restrict__ token_seq,
                                            const int* __restrict__ token_pos, const int* __restrict__ slot_of_seq,
                                            const float* __restrict__ gate, long long gate_stride, T* __restrict__ out,
                                            float* __restrict__ partial, int n_heads, int n_kv, int dk, int dv, int page_size,
-                                           int window, int keep_first, float scale, int sink) {
+                                           int window, int keep_first, float scale, int sink, ScoreOpts so) {
     extern __shared__ float smem[];
     const int n = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z, n_splits = gridDim.z;
     const int group = n_heads / n_kv;
@@ -180,7 +285,8 @@ __global__ void attention_sink_rows_kernel(const T* __restrict__ q, const T* __r
         __syncthreads();                               // the chunk buffers and qs of the heads before are done with
         if (active)
             for (int d = lane; d < dk; d += 32) qs[warp * dk + d] = to_f32(q[((size_t)n * n_heads + head) * dk + d]);
-        float m = with_sink ? 0.f : -INFINITY, l = with_sink ? 1.f : 0.f;
+        const float pre = scale * (active && so.head_scale ? so.head_scale[head] : 1.f);
+        float m = with_sink ? (active && so.sink_logit ? so.sink_logit[head] : 0.f) : -INFINITY, l = with_sink ? 1.f : 0.f;
         float acc[kMaxVRegs];
 #pragma unroll
         for (int i = 0; i < kMaxVRegs; ++i) acc[i] = 0.f;
@@ -211,7 +317,7 @@ __global__ void attention_sink_rows_kernel(const T* __restrict__ q, const T* __r
                     const float* kr = ks + lane * kstride;
                     const float* qr = qs + warp * dk;
                     for (int d = 0; d < dk; ++d) dot = fmaf(qr[d], kr[d], dot);
-                    s = dot * scale;
+                    s = capped(dot * pre, so.cap);
                 }
                 const float m_new = fmaxf(m, warp_max(s));      // finite: the chunk has a key
                 const float p = mine ? expf(s - m_new) : 0.f;
@@ -287,7 +393,7 @@ template <typename T>
 static int launch_rows(const void* q, const void* pool, long long page_elems, const int* block_table, int table_stride,
                        const int* token_seq, const int* token_pos, const int* slot_of_seq, const float* gate, long long gate_stride,
                        void* out, float* partial, int n_splits, int n_tokens, int n_heads, int n_kv, int dk, int dv, int page_size,
-                       int window, int keep_first, float scale, int sink, cudaStream_t stream) {
+                       int window, int keep_first, float scale, int sink, ScoreOpts so, cudaStream_t stream) {
     const int group = n_heads / n_kv;
     const int warps = group < 8 ? group : 8;
     const size_t smem = ((size_t)kChunk * (dk + 1) + (size_t)kChunk * dv + (size_t)warps * dk) * sizeof(float);
@@ -298,7 +404,7 @@ static int launch_rows(const void* q, const void* pool, long long page_elems, co
     }
     attention_sink_rows_kernel<T><<<dim3(n_tokens, n_kv, n_splits), warps * 32, smem, stream>>>(
         (const T*)q, (const T*)pool, page_elems, block_table, table_stride, token_seq, token_pos, slot_of_seq, gate, gate_stride,
-        (T*)out, partial, n_heads, n_kv, dk, dv, page_size, window, keep_first, scale, sink);
+        (T*)out, partial, n_heads, n_kv, dk, dv, page_size, window, keep_first, scale, sink, so);
     if (n_splits > 1) {
         const int items = n_tokens * n_heads;
         attention_sink_combine_kernel<T><<<(items + 3) / 4, 128, 0, stream>>>(partial, gate, gate_stride, (T*)out, n_tokens, n_heads, dv,
@@ -426,7 +532,8 @@ __global__ void __launch_bounds__(128 * HB) attention_sink_prompt_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ pool, long long page_elems,
     const int* __restrict__ block_table, int table_stride, const int* __restrict__ cu_seqlens, const int* __restrict__ start_pos,
     const int* __restrict__ slot_of_seq, int n_seqs, int n_tokens, const float* __restrict__ gate, long long gate_stride,
-    __nv_bfloat16* __restrict__ out, int n_heads, int n_kv, int dk, int dv, int window, int keep_first, float scale, int sink) {
+    __nv_bfloat16* __restrict__ out, int n_heads, int n_kv, int dk, int dv, int window, int keep_first, float scale, int sink,
+    ScoreOpts so) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ int found[3];
     const int tid = threadIdx.x, lane = tid & 31, warp = (tid >> 5) & 3, hb = tid >> 7;     // hb: which of the block's heads
@@ -491,9 +598,13 @@ __global__ void __launch_bounds__(128 * HB) attention_sink_prompt_kernel(
     const int quad = lane >> 2, pair = (lane & 3) * 2;
     const int lrow = lane & 7, lmat = lane >> 3;
     const int pr0 = p0 + warp * 16 + quad, pr1 = pr0 + 8;        // positions of this thread's two rows
-    const float scale2 = scale * 1.4426950408889634f;            // scores in units of log 2: the exponentials are exp2
+    // scores in units of log 2: the exponentials are exp2.  A cap (or a head's multiplier that is not positive, under which
+    // the largest raw score is not the largest score) is applied to the raw scores first, which are then in natural units.
+    const float pre = scale * (so.head_scale ? so.head_scale[head] : 1.f);
+    const bool shaped = so.cap > 0.f || !(pre > 0.f);
+    const float scale2 = (shaped ? 1.f : pre) * 1.4426950408889634f;
     float m[2], l[2], o[NV][4];
-    m[0] = m[1] = sink ? 0.f : -INFINITY;
+    m[0] = m[1] = sink ? (so.sink_logit ? so.sink_logit[head] * 1.4426950408889634f : 0.f) : -INFINITY;
     l[0] = l[1] = sink ? 0.25f : 0.f;                  // a quad's four lanes add up to the sink's one
 #pragma unroll
     for (int j = 0; j < NV; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
@@ -521,6 +632,12 @@ __global__ void __launch_bounds__(128 * HB) attention_sink_prompt_kernel(
                 mma_bf16(s[2 * jj], a, b[0], b[1]);
                 mma_bf16(s[2 * jj + 1], a, b[2], b[3]);
             }
+        }
+        if (shaped) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[j][e] = capped(s[j][e] * pre, so.cap);
         }
         float mx0 = -INFINITY, mx1 = -INFINITY;
         // every row of this warp sees every key of the page when the page lies behind the warp's first row and inside
@@ -616,7 +733,7 @@ template <int NV, int HB>
 static int launch_prompt(const void* q, const void* pool, long long page_elems, const int* block_table, int table_stride,
                          const int* cu_seqlens, const int* start_pos, const int* slot_of_seq, int n_seqs, const float* gate,
                          long long gate_stride, void* out, int n_tokens, int n_heads, int n_kv, int dk, int dv, int window,
-                         int keep_first, float scale, int sink, cudaStream_t stream) {
+                         int keep_first, float scale, int sink, ScoreOpts so, cudaStream_t stream) {
     const int dkp = (dk + 15) & ~15;
     const size_t smem = ((size_t)(HB + kPromptStages) * kTileQ * (dkp + 8) + (size_t)kPromptStages * kTileK * (8 * NV + 8)) * sizeof(__nv_bfloat16);
     if (smem > 48 * 1024) {
@@ -627,7 +744,7 @@ static int launch_prompt(const void* q, const void* pool, long long page_elems, 
     const unsigned tiles = (unsigned)((n_tokens + kTileQ - 1) / kTileQ + n_seqs);     // every sequence may end in a tile that is not full
     attention_sink_prompt_kernel<NV, HB><<<dim3(tiles, n_heads / HB), 128 * HB, smem, stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)pool, page_elems, block_table, table_stride, cu_seqlens, start_pos, slot_of_seq,
-        n_seqs, n_tokens, gate, gate_stride, (__nv_bfloat16*)out, n_heads, n_kv, dk, dv, window, keep_first, scale, sink);
+        n_seqs, n_tokens, gate, gate_stride, (__nv_bfloat16*)out, n_heads, n_kv, dk, dv, window, keep_first, scale, sink, so);
     return blm_check_launch("attention_sink (prompt)");
 }
 
@@ -640,7 +757,8 @@ __global__ void __launch_bounds__(128) attention_sink_decode_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ pool, long long page_elems,
     const int* __restrict__ block_table, int table_stride, const int* __restrict__ token_seq, const int* __restrict__ token_pos,
     const int* __restrict__ slot_of_seq, const float* __restrict__ gate, long long gate_stride, __nv_bfloat16* __restrict__ out,
-    float* __restrict__ partial, int n_heads, int n_kv, int dk, int dv, int window, int keep_first, float scale, int sink) {
+    float* __restrict__ partial, int n_heads, int n_kv, int dk, int dv, int window, int keep_first, float scale, int sink,
+    ScoreOpts so) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int n = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z, n_splits = gridDim.z;
@@ -689,10 +807,15 @@ __global__ void __launch_bounds__(128) attention_sink_decode_kernel(
     const int quad = lane >> 2, pair = (lane & 3) * 2;
     const int lrow = lane & 7, lmat = lane >> 3;
     const bool with_sink = sink && split == 0 && warp == 0;      // the sink is counted once
-    const float scale2 = scale * 1.4426950408889634f;            // scores in units of log 2: the exponentials are exp2
-    float m[2], l[2], o[NV][4];
-    m[0] = m[1] = with_sink ? 0.f : -INFINITY;
-    l[0] = l[1] = with_sink ? 0.25f : 0.f;
+    const float log2e = 1.4426950408889634f;                     // scores in units of log 2: the exponentials are exp2
+    float m[2], l[2], o[NV][4], pre[2];
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {                       // this thread's two rows are two heads of the group
+        const int r = quad + 8 * half;
+        pre[half] = scale * (so.head_scale && r < group ? so.head_scale[head0 + r] : 1.f);
+        m[half] = with_sink ? (so.sink_logit && r < group ? so.sink_logit[head0 + r] * log2e : 0.f) : -INFINITY;
+        l[half] = with_sink ? 0.25f : 0.f;
+    }
 #pragma unroll
     for (int j = 0; j < NV; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
     const unsigned qa = smem_at(Qs + (lrow + (lmat & 1) * 8) * qstride + (lmat >> 1) * 8);
@@ -723,7 +846,7 @@ __global__ void __launch_bounds__(128) attention_sink_decode_kernel(
             for (int e = 0; e < 4; ++e) {
                 const int key = pg * kTileK + 16 * warp + 8 * j + pair + (e & 1);
                 const bool sees = key <= pos && (pos - key < window || key < keep_first);
-                s[j][e] = sees ? s[j][e] * scale2 : -INFINITY;
+                s[j][e] = sees ? capped(s[j][e] * pre[e >> 1], so.cap) * log2e : -INFINITY;
             }
         float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
         float mx1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
@@ -815,7 +938,7 @@ template <int NV, int kDecodeStages>
 static int launch_decode(const void* q, const void* pool, long long page_elems, const int* block_table, int table_stride,
                          const int* token_seq, const int* token_pos, const int* slot_of_seq, const float* gate, long long gate_stride,
                          void* out, float* partial, int n_splits, int n_tokens, int n_heads, int n_kv, int dk, int dv, int window,
-                         int keep_first, float scale, int sink, cudaStream_t stream) {
+                         int keep_first, float scale, int sink, ScoreOpts so, cudaStream_t stream) {
     const int dkp = (dk + 15) & ~15;
     size_t smem = ((size_t)16 * (dkp + 8) + (size_t)kDecodeStages * kTileK * ((dkp + 8) + (8 * NV + 8))) * sizeof(__nv_bfloat16);
     const size_t merge = (size_t)16 * (dkp + 8) * sizeof(__nv_bfloat16) + (size_t)4 * 16 * (8 * NV + 2) * sizeof(float);
@@ -827,7 +950,7 @@ static int launch_decode(const void* q, const void* pool, long long page_elems, 
     cudaFuncSetAttribute(attention_sink_decode_kernel<NV, kDecodeStages>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     attention_sink_decode_kernel<NV, kDecodeStages><<<dim3(n_tokens, n_kv, n_splits), 128, smem, stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)pool, page_elems, block_table, table_stride, token_seq, token_pos, slot_of_seq, gate,
-        gate_stride, (__nv_bfloat16*)out, partial, n_heads, n_kv, dk, dv, window, keep_first, scale, sink);
+        gate_stride, (__nv_bfloat16*)out, partial, n_heads, n_kv, dk, dv, window, keep_first, scale, sink, so);
     if (n_splits > 1) {
         const int items = n_tokens * n_heads;
         attention_sink_combine_kernel<__nv_bfloat16><<<(items + 3) / 4, 128, 0, stream>>>(partial, gate, gate_stride, (__nv_bfloat16*)out,
@@ -876,8 +999,12 @@ BLM_API int blm_attention_sink(const void* q, const void* pool, int dtype, long 
                                int table_stride, const int* token_seq, const int* token_pos, const int* slot_of_seq,
                                const int* cu_seqlens, const int* start_pos, int n_seqs, int max_q_len, const float* gate,
                                long long gate_stride, void* out, float* partial, int n_splits, int n_tokens, int n_heads, int n_kv,
-                               int dk, int dv, int page_size, int window, int keep_first, float scale, int sink, cudaStream_t stream) {
+                               int dk, int dv, int page_size, int window, int keep_first, float scale, int sink,
+                               const float* head_scale, const float* sink_logit, float softcap, cudaStream_t stream) {
+    // head_scale, sink_logit: float32 [n_heads] or null; softcap: 0 for none (see ScoreOpts)
     if (n_tokens == 0) return BLM_OK;
+    const ScoreOpts so{head_scale, sink_logit, softcap};
+    BLM_REQUIRE(softcap >= 0.f, "attention_sink: a cap of %g", (double)softcap);
     BLM_REQUIRE(n_tokens > 0 && n_heads > 0 && n_kv > 0 && n_heads % n_kv == 0 && dk > 0 && dv > 0 && page_size > 0,
                 "attention_sink: bad sizes");
     BLM_REQUIRE(dv <= 32 * kMaxVRegs, "attention_sink: values of %d lanes; at most %d", dv, 32 * kMaxVRegs);
@@ -888,7 +1015,7 @@ BLM_API int blm_attention_sink(const void* q, const void* pool, int dtype, long 
     if (cu_seqlens != nullptr && start_pos != nullptr && n_seqs > 0 &&
         blm_attention_sink_prompt_takes(dtype, dk, dv, page_size, max_q_len, n_heads)) {
 #define BLM_PROMPT(NV) launch_prompt_heads<NV>(hb, q, pool, page_elems, block_table, table_stride, cu_seqlens, start_pos, slot_of_seq, n_seqs, gate, \
-                                         gate_stride, out, n_tokens, n_heads, n_kv, dk, dv, window, keep_first, scale, sink, stream)
+                                         gate_stride, out, n_tokens, n_heads, n_kv, dk, dv, window, keep_first, scale, sink, so, stream)
         const int group = n_heads / n_kv;
         int hb = BLM_PROMPT_HEADS;
         while (hb > 1 && (group % hb != 0 || (hb == 4 && dv > 64))) hb /= 2;    // four heads of 128 lanes would not fit the registers
@@ -899,7 +1026,7 @@ BLM_API int blm_attention_sink(const void* q, const void* pool, int dtype, long 
     }
     if (blm_attention_sink_decode_takes(dtype, dk, dv, page_size, n_heads, n_kv)) {
 #define BLM_DECODE(NV, STAGES) launch_decode<NV, STAGES>(q, pool, page_elems, block_table, table_stride, token_seq, token_pos, slot_of_seq, gate, gate_stride, \
-                                         out, partial, n_splits, n_tokens, n_heads, n_kv, dk, dv, window, keep_first, scale, sink, stream)
+                                         out, partial, n_splits, n_tokens, n_heads, n_kv, dk, dv, window, keep_first, scale, sink, so, stream)
         if (dv <= 32) return BLM_DECODE(4, 2);
         if (dv <= 64) return BLM_DECODE(8, 2);
         return BLM_DECODE(16, 3);
@@ -908,10 +1035,10 @@ BLM_API int blm_attention_sink(const void* q, const void* pool, int dtype, long 
     if (dtype == BLM_F32)
         return launch_rows<float>(q, pool, page_elems, block_table, table_stride, token_seq, token_pos, slot_of_seq, gate, gate_stride,
                                   out, partial, n_splits, n_tokens, n_heads, n_kv, dk, dv, page_size, window, keep_first, scale, sink,
-                                  stream);
+                                  so, stream);
     if (dtype == BLM_BF16)
         return launch_rows<__nv_bfloat16>(q, pool, page_elems, block_table, table_stride, token_seq, token_pos, slot_of_seq, gate,
                                           gate_stride, out, partial, n_splits, n_tokens, n_heads, n_kv, dk, dv, page_size, window,
-                                          keep_first, scale, sink, stream);
+                                          keep_first, scale, sink, so, stream);
     return blm_fail(BLM_BAD_ARGUMENT, "attention_sink: dtype %d", dtype);
 }

@@ -6,8 +6,11 @@
 //   expert(x) = W_down (silu(W_gate x) * (W_up x)).
 //   Options of the router: s = softmax(z) over all experts instead of the sigmoid; a correction [experts] added to the
 //   scores for the choice only (the weights are the scores without it); the chosen weights divided by their sum + 1e-20.
+//   A choice limited to groups: the experts form `n_groups` equal groups of neighbours, a group's mark is the sum of its
+//   two largest choice scores (with the correction), and only experts of the `keep_groups` groups of largest mark (ties:
+//   the lower index) can be chosen; the others' choice scores count as minus infinity.
 //   Option of the experts: the clamped gated unit, g = min(W_gate x, limit), u = clamp(W_up x, -limit, limit),
-//   g * sigmoid(alpha g) * (u + 1).
+//   g * sigmoid(alpha g) * (u + 1).  Or a unit without a gate, W_down act(W_up x), act the exact (erf) GELU or its tanh form.
 //
 // Everything runs on the device with sizes that depend on the step's token count only, so a step can be captured
 // in a CUDA graph: the grids cover the worst case (every expert's share padded to a tile) and blocks beyond the
@@ -22,11 +25,12 @@ BLM_API const char* blm_moe_last_error() { return g_blm_error; }
 template <typename T>
 __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, int width, int n_experts, int top,
                                  int* __restrict__ ids, float* __restrict__ weights, int softmax, const float* __restrict__ correction,
-                                 int renorm) {
+                                 int renorm, int n_groups, int keep_groups) {
     extern __shared__ float smem[];
     float* x = smem;                     // [width]
     float* score = smem + width;         // [n_experts]: what a chosen expert is weighted by
     float* choice = score + n_experts;   // [n_experts]: what the choice looks at (the score, plus the correction)
+    float* mark = choice + n_experts;    // [n_groups]: the groups' marks
     const int n = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
     for (int d = threadIdx.x; d < width; d += blockDim.x) x[d] = to_f32(h[(size_t)n * width + d]);
@@ -56,6 +60,26 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
         }
         for (int e = lane; e < n_experts; e += 32) choice[e] = correction ? score[e] + correction[e] : score[e];
         __syncwarp();
+        if (n_groups > 1 && keep_groups < n_groups) {
+            const int per = n_experts / n_groups;
+            for (int g = lane; g < n_groups; g += 32) {          // a group's mark: its two largest choice scores
+                float a = -INFINITY, b = -INFINITY;
+                for (int e = g * per; e < (g + 1) * per; ++e) {
+                    const float c = choice[e];
+                    if (c > a) { b = a; a = c; } else if (c > b) b = c;
+                }
+                mark[g] = per > 1 ? a + b : a;
+            }
+            __syncwarp();
+            for (int g = lane; g < n_groups; g += 32) {          // kept when fewer than keep_groups groups come before it
+                const float mine = mark[g];
+                int ahead = 0;
+                for (int o = 0; o < n_groups; ++o) ahead += (mark[o] > mine || (mark[o] == mine && o < g)) ? 1 : 0;
+                if (ahead >= keep_groups)
+                    for (int e = g * per; e < (g + 1) * per; ++e) choice[e] = -INFINITY;
+            }
+            __syncwarp();
+        }
         float total = 0.f;
         for (int k = 0; k < top; ++k) {
             float best = -INFINITY;
@@ -86,17 +110,23 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
 }
 
 BLM_API int blm_moe_route(const void* h, int dtype, const float* router, int n_tokens, int width, int n_experts, int top, int* ids,
-                          float* weights, int softmax, const float* correction, int renorm, cudaStream_t stream) {
+                          float* weights, int softmax, const float* correction, int renorm, int n_groups, int keep_groups,
+                          cudaStream_t stream) {
+    // n_groups <= 1: the choice is among all experts
     if (n_tokens == 0) return BLM_OK;
     BLM_REQUIRE(n_tokens > 0 && width > 0 && n_experts > 0 && top > 0 && top <= n_experts, "moe_route: bad sizes");
-    const size_t smem = ((size_t)width + 2 * n_experts) * sizeof(float);
+    if (n_groups < 1) n_groups = 1;
+    BLM_REQUIRE(n_experts % n_groups == 0 && keep_groups >= 1 && keep_groups <= n_groups &&
+                (long long)keep_groups * (n_experts / n_groups) >= top,
+                "moe_route: %d experts in %d groups of which %d are kept, for %d chosen", n_experts, n_groups, keep_groups, top);
+    const size_t smem = ((size_t)width + 2 * n_experts + n_groups) * sizeof(float);
     BLM_REQUIRE(smem <= 48 * 1024, "moe_route: width %d and %d experts need %zu bytes of shared memory", width, n_experts, smem);
     if (dtype == BLM_F32)
         moe_route_kernel<float><<<n_tokens, 128, smem, stream>>>((const float*)h, router, width, n_experts, top, ids, weights, softmax,
-                                                                 correction, renorm);
+                                                                 correction, renorm, n_groups, keep_groups);
     else if (dtype == BLM_BF16)
         moe_route_kernel<__nv_bfloat16><<<n_tokens, 128, smem, stream>>>((const __nv_bfloat16*)h, router, width, n_experts, top, ids,
-                                                                         weights, softmax, correction, renorm);
+                                                                         weights, softmax, correction, renorm, n_groups, keep_groups);
     else
         return blm_fail(BLM_BAD_ARGUMENT, "moe_route: dtype %d", dtype);
     return blm_check_launch("moe_route");
@@ -173,12 +203,16 @@ __device__ __forceinline__ bool moe_find_tile(const int* __restrict__ offsets, i
 // x rounded as the activations' dtype rounds it: the input of a product in that dtype
 template <typename T> __device__ __forceinline__ float as_input(float v) { return to_f32(from_f32<T>(v)); }
 
-// The gated unit of an expert.  limit <= 0: silu(g) * u.  limit > 0, the clamped unit: g = min(g, limit), u = clamp(u, -limit, limit),
-// g * sigmoid(alpha g) * (u + 1).
+// The unit of an expert.  plain 0, the gated units: limit <= 0: silu(g) * u; limit > 0, the clamped unit: g = min(g, limit),
+// u = clamp(u, -limit, limit), g * sigmoid(alpha g) * (u + 1).  plain 1 and 2, the units without a gate (the weight then
+// holds the up rows only, and u is not computed): the exact GELU, g (1 + erf(g / sqrt 2)) / 2, and its tanh form.
 struct GluAct {
     float limit, alpha;
+    int plain;
 };
 __device__ __forceinline__ float glu_act(float g, float u, GluAct a) {
+    if (a.plain == 1) return 0.5f * g * (1.0f + erff(g * 0.70710678118654752f));
+    if (a.plain == 2) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
     if (a.limit <= 0.f) return g / (1.0f + expf(-g)) * u;
     g = fminf(g, a.limit);
     u = fminf(fmaxf(u, -a.limit), a.limit);
@@ -211,7 +245,8 @@ __global__ void moe_gate_up_kernel(const T* __restrict__ h, const float* __restr
         scale_of[threadIdx.x] = sc;
     }
     __syncthreads();
-    const T* wg = w_gu + (size_t)e * 2 * ff * width;
+    const bool gated = glu.plain == 0;
+    const T* wg = w_gu + (size_t)e * (gated ? 2 : 1) * ff * width;
     const T* wu = wg + (size_t)ff * width;
     float ag[2][2] = {{0.f, 0.f}, {0.f, 0.f}}, au[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
     for (int k0 = 0; k0 < width; k0 += kBK) {
@@ -229,7 +264,7 @@ __global__ void moe_gate_up_kernel(const T* __restrict__ h, const float* __restr
             const int r = idx / kBK, kk = idx % kBK, k = k0 + kk, c = c0 + r;
             const bool in = c < ff && k < width;
             gs[r][kk] = in ? to_f32(wg[(size_t)c * width + k]) : 0.f;
-            us[r][kk] = in ? to_f32(wu[(size_t)c * width + k]) : 0.f;
+            us[r][kk] = in && gated ? to_f32(wu[(size_t)c * width + k]) : 0.f;
         }
         __syncthreads();
 #pragma unroll
@@ -360,6 +395,7 @@ __device__ __forceinline__ void moe_warp_product2(float (&g)[8][4], float (&u)[8
     }
 }
 
+template <bool kGated>
 __global__ void __launch_bounds__(128) moe_gate_up_tc_kernel(const __nv_bfloat16* __restrict__ h, const float* __restrict__ weights,
                                                              const int* __restrict__ order, const int* __restrict__ offsets,
                                                              const __nv_bfloat16* __restrict__ w_gu, __nv_bfloat16* __restrict__ act,
@@ -386,7 +422,7 @@ __global__ void __launch_bounds__(128) moe_gate_up_tc_kernel(const __nv_bfloat16
         scale_of[threadIdx.x] = sc;
     }
     __syncthreads();
-    const __nv_bfloat16* wg = w_gu + (size_t)e * 2 * ff * width;
+    const __nv_bfloat16* wg = w_gu + (size_t)e * (kGated ? 2 : 1) * ff * width;
     const __nv_bfloat16* wu = wg + (size_t)ff * width;
     auto stage_slice = [&](int buf, int k0) {
         __nv_bfloat16* xs = stage + buf * 3 * kTile;
@@ -397,7 +433,7 @@ __global__ void __launch_bounds__(128) moe_gate_up_tc_kernel(const __nv_bfloat16
             moe_cp16(xs + r * kTStride + kk, in ? h + (size_t)tok * width + k0 + kk : h, in);
         }
         moe_stage_weight(xs + kTile, wg, ff, width, c0, k0);
-        moe_stage_weight(xs + 2 * kTile, wu, ff, width, c0, k0);
+        if (kGated) moe_stage_weight(xs + 2 * kTile, wu, ff, width, c0, k0);
     };
     float g[8][4], u[8][4];
 #pragma unroll
@@ -415,7 +451,8 @@ __global__ void __launch_bounds__(128) moe_gate_up_tc_kernel(const __nv_bfloat16
         moe_cp_wait_all_but_one();
         __syncthreads();
         const unsigned xs = stage_at + buf * 3 * kTile * 2;
-        moe_warp_product2(g, u, xs + a_off * 2, xs + (kTile + b_off) * 2, xs + (2 * kTile + b_off) * 2);
+        if (kGated) moe_warp_product2(g, u, xs + a_off * 2, xs + (kTile + b_off) * 2, xs + (2 * kTile + b_off) * 2);
+        else moe_warp_product(g, xs + a_off * 2, xs + (kTile + b_off) * 2);
         __syncthreads();
     }
     const int r0 = warp * 16 + quad, r1 = r0 + 8;
@@ -491,11 +528,13 @@ __global__ void __launch_bounds__(128) moe_down_tc_kernel(const __nv_bfloat16* _
 
 BLM_API int blm_moe_experts(const void* h, int dtype, const float* weights, const int* order, const int* offsets, const void* w_gu,
                             const void* w_down, void* act, float* y, int n_tokens, int width, int ff, int n_experts, int top,
-                            int scale_input, float act_limit, float act_alpha, cudaStream_t stream) {
-    // act_limit <= 0: the experts' unit is silu(gate) * up; > 0: the clamped unit with that limit and act_alpha
+                            int scale_input, float act_limit, float act_alpha, int plain_unit, cudaStream_t stream) {
+    // plain_unit 0: the gated units, w_gu [experts][2 ff][width]; act_limit <= 0: silu(gate) * up; > 0: the clamped unit with
+    // that limit and act_alpha.  plain_unit 1 (exact GELU) or 2 (tanh GELU): no gate, w_gu [experts][ff][width]
     if (n_tokens == 0) return BLM_OK;
     BLM_REQUIRE(n_tokens > 0 && width > 0 && ff > 0 && n_experts > 0 && top > 0, "moe_experts: bad sizes");
-    const GluAct glu{act_limit, act_alpha};
+    BLM_REQUIRE(plain_unit >= 0 && plain_unit <= 2, "moe_experts: unit %d", plain_unit);
+    const GluAct glu{act_limit, act_alpha, plain_unit};
     const long long pairs = (long long)n_tokens * top;
     const long long tiles = (pairs + kBM - 1) / kBM + n_experts;      // every expert's share may end in a tile that is not full
     BLM_REQUIRE(tiles < (1ll << 31), "moe_experts: %lld tiles", tiles);
@@ -509,10 +548,11 @@ BLM_API int blm_moe_experts(const void* h, int dtype, const float* weights, cons
         const long long t64 = (pairs + kTM - 1) / kTM + n_experts;
         const dim3 t1((unsigned)t64, (unsigned)((ff + kTN - 1) / kTN)), t2((unsigned)t64, (unsigned)((width + kTN - 1) / kTN));
         const int smem1 = 2 * 3 * kTile * (int)sizeof(__nv_bfloat16), smem2 = 2 * 2 * kTile * (int)sizeof(__nv_bfloat16);
-        cudaError_t err = cudaFuncSetAttribute(moe_gate_up_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1);
+        auto up_kernel = plain_unit ? moe_gate_up_tc_kernel<false> : moe_gate_up_tc_kernel<true>;
+        cudaError_t err = cudaFuncSetAttribute(up_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1);
         if (err != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "moe_experts: %s", cudaGetErrorString(err));
-        moe_gate_up_tc_kernel<<<t1, 128, smem1, stream>>>((const __nv_bfloat16*)h, weights, order, offsets, (const __nv_bfloat16*)w_gu,
-                                                          (__nv_bfloat16*)act, width, ff, n_experts, top, scale_input, glu);
+        up_kernel<<<t1, 128, smem1, stream>>>((const __nv_bfloat16*)h, weights, order, offsets, (const __nv_bfloat16*)w_gu,
+                                              (__nv_bfloat16*)act, width, ff, n_experts, top, scale_input, glu);
         moe_down_tc_kernel<<<t2, 128, smem2, stream>>>((const __nv_bfloat16*)act, offsets, (const __nv_bfloat16*)w_down, y, width, ff,
                                                        n_experts);
     } else if (dtype == BLM_BF16) {

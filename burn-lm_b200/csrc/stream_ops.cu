@@ -38,6 +38,7 @@ BLM_API int blm_embed_scaled(const int* tokens, const void* table, int table_dty
 // mixers that ran side by side:
 //     h   = resid + mult * (d / sqrt(mean(d^2) + eps_post) * post_w)          (stored unless `rows`)
 //     out = h / sqrt(mean(h^2) + eps_pre) * pre_w                             (when pre_w is given)
+//     out = h, converted to out's type                                        (out without pre_w: a sublayer reads the stream itself)
 // delta null: h = resid.  rows given: row b of `out` comes from row rows[b]; the stream is left alone.
 // ---------------------------------------------------------------------------------------------
 template <typename TD, typename TA>
@@ -75,7 +76,12 @@ __global__ void sandwich_norm_kernel(float* __restrict__ resid, const TD* __rest
         row_buf[d] = h;
         ss += h * h;
     }
-    if (pre_w == nullptr || out == nullptr) return;
+    if (out == nullptr) return;
+    if (pre_w == nullptr) {
+        TA* o = out + (size_t)blockIdx.x * width;
+        for (int d = threadIdx.x; d < width; d += blockDim.x) o[d] = from_f32<TA>(row_buf[d]);
+        return;
+    }
     const float total = block_sum(ss, red);
     const float inv = 1.0f / sqrtf(total / (float)width + eps_pre);
     TA* o = out + (size_t)blockIdx.x * width;

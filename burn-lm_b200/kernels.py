@@ -93,7 +93,10 @@ _protos = {
                                c_void_p, c_int, c_void_p],
         "blm_attention_sink": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                c_void_p, c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                               c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+                               c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_float, c_void_p],
+        "blm_head_norm_rope_append": [c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_int,
+                                      c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_longlong, c_int, c_void_p, c_void_p,
+                                      c_void_p, c_void_p, c_int, c_void_p],
         "blm_attention_sink_prompt_takes": [c_int, c_int, c_int, c_int, c_int, c_int],
         "blm_attention_sink_decode_takes": [c_int, c_int, c_int, c_int, c_int, c_int],
     },
@@ -136,21 +139,23 @@ _protos = {
     "attention_latent": {
         "blm_latent_prepare": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_float, c_void_p, c_int, c_void_p, c_void_p,
                                c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                               c_int, c_int, c_void_p],
+                               c_int, c_int, c_int, c_void_p],
         "blm_latent_gather": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                              c_void_p],
+                              c_int, c_void_p],
         "blm_latent_expand": [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                               c_void_p],
         "blm_latent_attention": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                 c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+                                 c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p,
+                                 c_void_p],
         "blm_latent_attention_tile_rows": [c_int, c_int, c_int, c_int, c_int],
-        "blm_sigmoid_gate": [c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_void_p],
+        "blm_sigmoid_gate": [c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p],
     },
     "moe": {
-        "blm_moe_route": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p],
+        "blm_moe_route": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+                          c_void_p],
         "blm_moe_group": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
         "blm_moe_experts": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                            c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
+                            c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p],
         "blm_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     },
     "attention": {
@@ -381,6 +386,33 @@ def qk_norm_append(proj, step, pool, block_table, q_out, n_heads, n_kv, key_dim,
           _ptr(block_table), block_table.shape[1], _stream())
 
 
+def head_norm_rope_append(proj, step, pool, block_table, q_out, n_heads, n_kv, key_dim, value_dim, q_weight=None, k_weight=None,
+                          eps=0.0, value_norm=False, freq=None, rotary_dims=0, halves=False):
+    """What follows a fused projection [q | k | v | ...] (float32 [N, >= (n_heads + n_kv) key_dim + n_kv value_dim]), head by
+    head: every head of q is divided by its root mean square (eps inside the root) and multiplied by `q_weight` (float32
+    [key_dim], the same for all heads; None: q stays as it is), every head of k likewise with `k_weight`; the first
+    `rotary_dims` lanes of every q and k head turn by position * freq[i] (freq float64 [rotary_dims / 2]), lanes (2i, 2i + 1)
+    together, or (i, i + rotary_dims / 2) with `halves`; with `value_norm` every head of v is divided by its root mean square
+    (no weight).  q goes to `q_out` [N, n_heads key_dim], k and v to the token's place in the paged cache."""
+    _need_cuda(proj, pool, block_table, q_out, q_weight, k_weight, freq)
+    _f32(proj, q_weight, k_weight)
+    n = proj.shape[0]
+    qc, kc, vc = n_heads * key_dim, n_kv * key_dim, n_kv * value_dim
+    if proj.dim() != 2 or proj.shape[1] < qc + kc + vc or proj.stride(1) != 1:
+        raise KernelError("head_norm_rope_append: the projection is float32 [N, q + k + v (+ more)]")
+    if tuple(q_out.shape) != (n, qc) or q_out.dtype != pool.dtype or not q_out.is_contiguous():
+        raise KernelError("head_norm_rope_append: q_out must be [N, heads * key_dim] in the cache's dtype")
+    for t in (q_weight, k_weight):
+        if t is not None and t.numel() != key_dim:
+            raise KernelError("head_norm_rope_append: the norms' weights are float32 [key_dim]")
+    if rotary_dims and (freq is None or freq.dtype != torch.float64 or freq.numel() != rotary_dims // 2):
+        raise KernelError("head_norm_rope_append: freq must be float64 [rotary_dims / 2]")
+    _call("attention_sink", "blm_head_norm_rope_append", _ptr(proj), c_longlong(proj.stride(0)), n, n_heads, n_kv, key_dim, value_dim,
+          _ptr(q_weight), _ptr(k_weight), c_float(eps), 1 if value_norm else 0, _ptr(freq), int(rotary_dims), 1 if halves else 0,
+          _ptr(q_out), _ptr(pool), _code(pool.dtype), c_longlong(_flat_pool(pool, n_kv, key_dim, value_dim)), PAGE, _ptr(step.token_seq),
+          _ptr(step.token_pos), _ptr(step.slot_of_seq), _ptr(block_table), block_table.shape[1], _stream())
+
+
 def attention_sink_scratch_floats(n_tokens, n_heads, value_dim, n_splits) -> int:
     return 0 if n_splits <= 1 else n_tokens * n_heads * n_splits * (value_dim + 2)
 
@@ -397,19 +429,26 @@ def attention_sink_decode_takes(dtype, key_dim, value_dim, n_heads, n_kv) -> boo
 
 
 def attention_sink(q, step, pool, block_table, out, n_heads, n_kv, key_dim, value_dim, scale, window, keep_first=0, sink=True,
-                   gate=None, gate_stride=0, max_q_len=1, n_splits=1, scratch=None):
+                   gate=None, gate_stride=0, max_q_len=1, n_splits=1, scratch=None, head_scale=None, sink_logit=None, softcap=0.0):
     """Attention of the step's tokens over the paged cache (after the append) where the query at position i sees the
     key at j when j <= i and (i - j < window or j < keep_first); softmax with `sink` added to its denominator (one more
     entry of score 0 without a value); keys of `key_dim` and values of `value_dim` lanes; `gate`: a float32 tensor
     whose element n * gate_stride + h is squashed by a sigmoid and multiplies head h's output of token n.
     q [N, n_heads key_dim] and out [N, n_heads value_dim] in the cache's dtype.
+    `head_scale` float32 [n_heads]: head h's scores are scale * head_scale[h] * q.k; `softcap` > 0: a score s becomes
+    softcap * tanh(s / softcap) before the softmax; `sink_logit` float32 [n_heads]: the sink's score is that number instead
+    of 0 (exp(sink_logit[h]) joins the denominator).
 
     `max_q_len`: the longest run of new tokens of one sequence (a bound is enough): bfloat16 steps of 8 or more run
     the tensor-core prompt kernel, 64 query rows a block (it reads step.cu_seqlens and step.start_pos); shorter ones
     the tensor-core decode kernel (bfloat16, up to 16 query heads a kv head) or else the row kernel, a block per (row,
     kv head) either, whose keys `n_splits` > 1 cuts over that many blocks (it then needs `scratch`:
     attention_sink_scratch_floats(...) float32)."""
-    _need_cuda(q, pool, block_table, out, scratch)
+    _need_cuda(q, pool, block_table, out, scratch, head_scale, sink_logit)
+    _f32(head_scale, sink_logit)
+    for t in (head_scale, sink_logit):
+        if t is not None and t.numel() != n_heads:
+            raise KernelError("attention_sink: head_scale and sink_logit have a number per query head")
     n = q.shape[0]
     if tuple(q.shape) != (n, n_heads * key_dim) or tuple(out.shape) != (n, n_heads * value_dim) or q.dtype != pool.dtype \
             or out.dtype != pool.dtype:
@@ -428,14 +467,17 @@ def attention_sink(q, step, pool, block_table, out, n_heads, n_kv, key_dim, valu
           _ptr(block_table), block_table.shape[1], _ptr(step.token_seq), _ptr(step.token_pos), _ptr(step.slot_of_seq), _ptr(cu),
           _ptr(step.start_pos if prompt else None), (cu.numel() - 1) if prompt else 0, int(max_q_len), _ptr(gate), int(gate_stride),
           _ptr(out), _ptr(scratch), int(n_splits), n, n_heads, n_kv, key_dim, value_dim, PAGE, int(window), int(keep_first),
-          c_float(scale), 1 if sink else 0, _stream(), kernels=2 if n_splits > 1 else 1)
+          c_float(scale), 1 if sink else 0, _ptr(head_scale), _ptr(sink_logit if sink else None), c_float(softcap or 0.0), _stream(),
+          kernels=2 if n_splits > 1 else 1)
 
 
-def moe_route(h, router, top, softmax=False, correction=None, renormalise=False):
+def moe_route(h, router, top, softmax=False, correction=None, renormalise=False, n_groups=1, keep_groups=1):
     """(ids int32 [N, top], weights float32 [N, top]): every token's `top` experts of largest sigmoid(router h), in
     falling order (the lower index on a tie), with those scores.  router float32 [experts, D]; sums in float32.
     `softmax`: the scores are softmax(router h) over all experts.  `correction` float32 [experts]: added to the scores for
-    the choice only; the weights stay the scores.  `renormalise`: the chosen weights are divided by their sum + 1e-20."""
+    the choice only; the weights stay the scores.  `renormalise`: the chosen weights are divided by their sum + 1e-20.
+    `n_groups` > 1: the experts form that many equal groups of neighbours, a group's mark is the sum of its two largest
+    choice scores (correction included), and only experts of the `keep_groups` groups of largest mark can be chosen."""
     _need_cuda(h, router, correction)
     _f32(correction)
     if correction is not None and correction.numel() != router.shape[0]:
@@ -446,23 +488,29 @@ def moe_route(h, router, top, softmax=False, correction=None, renormalise=False)
     ids = torch.empty((n, top), dtype=torch.int32, device=h.device)
     weights = torch.empty((n, top), dtype=torch.float32, device=h.device)
     _call("moe", "blm_moe_route", _ptr(h), _code(h.dtype), _ptr(router), n, d, router.shape[0], top, _ptr(ids), _ptr(weights),
-          1 if softmax else 0, _ptr(correction), 1 if renormalise else 0, _stream())
+          1 if softmax else 0, _ptr(correction), 1 if renormalise else 0, int(n_groups), int(keep_groups if n_groups > 1 else 1), _stream())
     return ids, weights
 
 
-def moe_experts(h, ids, weights, gate_up, down, extra=None, weight_on_input=True, clamp_limit=0.0, clamp_alpha=1.702, out_dtype=None):
+UNIT_GATED, UNIT_GELU, UNIT_GELU_TANH = 0, 1, 2      # an expert's unit: gated (silu or clamped); W_down gelu(W_up x), exact or tanh form
+
+
+def moe_experts(h, ids, weights, gate_up, down, extra=None, weight_on_input=True, clamp_limit=0.0, clamp_alpha=1.702, out_dtype=None,
+                unit=UNIT_GATED):
     """sum over a token's chosen experts of expert(weight h) (`weight_on_input`) or of weight expert(h), plus `extra`
     [N, D] when given; expert(x) = down[e] (silu(gate[e] x) * (up[e] x)).  gate_up [experts, 2 ff, D] (an expert's
     gate rows, then its up rows) and down [experts, D, ff] in h's dtype.  Returns [N, D] in h's dtype, or in float32
     (`out_dtype`).  `clamp_limit` > 0: the experts' unit is the clamped one, g = min(gate x, limit), u = clamp(up x, -limit,
-    limit), g sigmoid(clamp_alpha g) (u + 1)."""
+    limit), g sigmoid(clamp_alpha g) (u + 1).  `unit` UNIT_GELU or UNIT_GELU_TANH: the experts have no gate,
+    expert(x) = down[e] gelu(up[e] x), and `gate_up` is [experts, ff, D], the up rows alone."""
     _need_cuda(h, ids, weights, gate_up, down, extra)
     n, d = h.shape
     top = ids.shape[1]
-    e, two_ff, _ = gate_up.shape
-    ff = two_ff // 2
-    if gate_up.dtype != h.dtype or down.dtype != h.dtype or tuple(gate_up.shape) != (e, 2 * ff, d) or tuple(down.shape) != (e, d, ff):
-        raise KernelError("moe_experts: gate_up [experts, 2 ff, D] and down [experts, D, ff] in the activations' dtype")
+    e, rows, _ = gate_up.shape
+    ff = rows // 2 if unit == UNIT_GATED else rows
+    if (gate_up.dtype != h.dtype or down.dtype != h.dtype or tuple(gate_up.shape) != (e, (2 if unit == UNIT_GATED else 1) * ff, d)
+            or tuple(down.shape) != (e, d, ff)):
+        raise KernelError("moe_experts: gate_up [experts, 2 ff, D] (ff rows without a gate) and down [experts, D, ff] in the activations' dtype")
     if ids.dtype != torch.int32 or weights.dtype != torch.float32 or tuple(weights.shape) != (n, top):
         raise KernelError("moe_experts: ids int32 [N, top], weights float32 [N, top]")
     if extra is not None and (extra.dtype != h.dtype or tuple(extra.shape) != (n, d)):
@@ -478,7 +526,7 @@ def moe_experts(h, ids, weights, gate_up, down, extra=None, weight_on_input=True
     stream = _stream()
     _call("moe", "blm_moe_group", _ptr(ids), pairs, e, _ptr(offsets), _ptr(order), _ptr(place_of), stream)
     _call("moe", "blm_moe_experts", _ptr(h), _code(h.dtype), _ptr(weights), _ptr(order), _ptr(offsets), _ptr(gate_up), _ptr(down),
-          _ptr(act), _ptr(y), n, d, ff, e, top, 1 if weight_on_input else 0, c_float(clamp_limit), c_float(clamp_alpha), stream, kernels=2)
+          _ptr(act), _ptr(y), n, d, ff, e, top, 1 if weight_on_input else 0, c_float(clamp_limit), c_float(clamp_alpha), int(unit), stream, kernels=2)
     _call("moe", "blm_moe_combine", _ptr(y), _ptr(place_of), _ptr(weights), _ptr(extra), _ptr(out), _code(h.dtype), n, d, top,
           0 if weight_on_input else 1, _code(out.dtype), stream)
     return out
@@ -1019,6 +1067,7 @@ def sandwich_norm(resid, delta, post_weight, mult, eps_post, pre_weight, eps_pre
 
         h   = resid + mult * (d / sqrt(mean(d^2) + eps_post) * post_weight)       stored into resid (rows is None)
         out = h / sqrt(mean(h^2) + eps_pre) * pre_weight                          when pre_weight and out are given
+        out = h in out's dtype                                                    when out is given without pre_weight
 
     delta None: h = resid.  rows (int32 [R]): row i of out comes from row rows[i], resid is left alone.
     resid fp32 [N, D]; delta [N, D] in float32 or bfloat16; the weights and the bias float32 [D]."""
@@ -1028,8 +1077,8 @@ def sandwich_norm(resid, delta, post_weight, mult, eps_post, pre_weight, eps_pre
     n_out = rows.numel() if rows is not None else resid.shape[0]
     if delta is not None and (delta.shape != resid.shape or post_weight is None or post_weight.numel() != d):
         raise KernelError("sandwich_norm: delta must match resid's shape and bring its norm's weight [D]")
-    if out is not None and (tuple(out.shape) != (n_out, d) or pre_weight is None or pre_weight.numel() != d):
-        raise KernelError("sandwich_norm: out [rows, D] needs the weight [D] of the norm that produces it")
+    if out is not None and (tuple(out.shape) != (n_out, d) or (pre_weight is not None and pre_weight.numel() != d)):
+        raise KernelError("sandwich_norm: out [rows, D]; the weight [D] of the norm that produces it, or none for the stream as it is")
     if rows is not None and rows.dtype != torch.int32:
         raise KernelError("sandwich_norm: rows must be int32")
     sa, delta_b, sb = second if second is not None else (1.0, None, 0.0)
@@ -1281,14 +1330,15 @@ def sigmoid_attention(q, pool, block_table, step, out, n_heads, n_kv, key_dim, v
 # attention over a cached latent
 # ------------------------------------------------------------------------------------------------
 def latent_prepare(q_proj, down, c_weight, eps, freq, rot_dims, q_nope, q_rot, pool, block_table, step, n_heads, key_dim, rot_dim,
-                   rank, q_full=None):
+                   rank, q_full=None, halves=False):
     """q_proj float32 [N, heads * (key_dim + rot_dim)] (every head's unrotated lanes, then its rotated ones) and down
     float32 [N, rank + rot_dim]: q_nope [heads, N, key_dim] (the cache's dtype) takes the unrotated lanes, q_rot float32
     [N, heads, rot_dim] the rotated ones turned by the token's position (lanes 2i, 2i + 1 by position * freq[i] for the first
     rot_dims lanes; freq float64 [rot_dims / 2]); the first `rank` lanes of `down`, RMS-normed with c_weight, and its last
     rot_dim lanes, turned likewise, go to the token's place in the paged cache ([pages, PAGE, rank + rot_dim]).
     With `q_full` [N, heads, hd] (the cache's dtype, hd >= key_dim + rot_dim) the query goes there instead, a head's
-    unrotated lanes, its turned ones and zeros side by side, and q_nope and q_rot are not written (they may be None)."""
+    unrotated lanes, its turned ones and zeros side by side, and q_nope and q_rot are not written (they may be None).
+    `halves`: the turning lanes are paired (i, i + rot_dims / 2) instead of (2i, 2i + 1)."""
     _need_cuda(c_weight, freq, q_nope, q_rot, q_full, pool, block_table)
     _f32(q_proj, down, c_weight, q_rot)
     if not q_proj.is_cuda or not down.is_cuda or q_proj.stride(1) != 1 or down.stride(1) != 1:
@@ -1311,12 +1361,13 @@ def latent_prepare(q_proj, down, c_weight, eps, freq, rot_dims, q_nope, q_rot, p
     _call("attention_latent", "blm_latent_prepare", _ptr(q_proj), c_longlong(q_proj.stride(0)), _ptr(down), c_longlong(down.stride(0)),
           _ptr(c_weight), c_float(eps), _ptr(freq), int(rot_dims), _ptr(q_nope), _ptr(q_rot), _ptr(q_full), int(hd_full), _ptr(pool),
           _code(pool.dtype), _ptr(step.token_seq), _ptr(step.token_pos), _ptr(step.slot_of_seq), _ptr(block_table), block_table.shape[1],
-          n, n_heads, key_dim, rot_dim, rank, PAGE, _stream())
+          n, n_heads, key_dim, rot_dim, rank, PAGE, 1 if halves else 0, _stream())
 
 
-def latent_gather(pool, block_table, step, out, pages_each, lanes):
+def latent_gather(pool, block_table, step, out, pages_each, lanes, window=0):
     """The cached pages of the step's sequences side by side: out [n_seqs * pages_each, PAGE, lanes] takes page p of
-    sequence s at s * pages_each + p; positions a sequence has not reached are zeros."""
+    sequence s at s * pages_each + p; positions a sequence has not reached are zeros.  `window` > 0: so are the pages
+    that lie wholly before the window of the step's first token (the cache may have given them back)."""
     _need_cuda(pool, block_table, out)
     if out.dtype != pool.dtype or out.numel() != step.n_seqs * pages_each * PAGE * lanes or not out.is_contiguous():
         raise KernelError("latent_gather: out [n_seqs * pages_each, PAGE, lanes] in the cache's dtype")
@@ -1324,7 +1375,7 @@ def latent_gather(pool, block_table, step, out, pages_each, lanes):
         raise KernelError("latent_gather: the pool's pages are [PAGE, lanes]; a sequence has at most the table's pages")
     _call("attention_latent", "blm_latent_gather", _ptr(pool), _code(pool.dtype), _ptr(block_table), block_table.shape[1],
           _ptr(step.cu_seqlens), _ptr(step.slot_of_seq), _ptr(step.start_pos), _ptr(out), step.n_seqs, int(pages_each), int(lanes), PAGE,
-          _stream())
+          int(window), _stream())
 
 
 def latent_expand(kv, gathered, out, n_heads, key_dim, rot_dim, value_dim, rank):
@@ -1353,14 +1404,19 @@ def latent_attention_tile_rows(dtype, n_heads, rank, rot_dim, max_q_len) -> int:
     return int(_lib("attention_latent").blm_latent_attention_tile_rows(_code(dtype), n_heads, rank, rot_dim, max_q_len))
 
 
-def latent_attention(q_lat, q_rot, pool, block_table, step, out, n_heads, rank, rot_dim, scale, n_splits=1, partial=None):
+def latent_attention(q_lat, q_rot, pool, block_table, step, out, n_heads, rank, rot_dim, scale, n_splits=1, partial=None,
+                     window=0, sink=None):
     """Causal softmax attention of every new token's heads over its sequence's cached positions, each one key of rank +
     rot_dim lanes shared by the heads, whose first `rank` lanes are the value: score = (q_lat . c + q_rot . k_rot) * scale.
     q_lat float32 [heads, N, rank], q_rot float32 [N, heads, rot_dim]; out [heads, N, rank] in float32 or the cache's dtype
     (rows of no sequence are left as they are).  `n_splits` > 1 cuts every row's keys over that many blocks (`partial`:
-    float32 scratch of latent_attention_scratch_floats) whose shares are merged in order."""
-    _need_cuda(q_lat, q_rot, pool, block_table, out, partial)
-    _f32(q_lat, q_rot, partial)
+    float32 scratch of latent_attention_scratch_floats) whose shares are merged in order.  `window` > 0: position i sees
+    j with 0 <= i - j < window.  `sink` float32 [heads]: exp(sink_h) joins the softmax's denominator (no key, no value,
+    not scaled)."""
+    _need_cuda(q_lat, q_rot, pool, block_table, out, partial, sink)
+    _f32(q_lat, q_rot, partial, sink)
+    if sink is not None and sink.numel() != n_heads:
+        raise KernelError("latent_attention: the sink has a number per head")
     n = step.n_tokens
     if tuple(q_lat.shape) != (n_heads, n, rank) or tuple(q_rot.shape) != (n, n_heads, rot_dim) or tuple(out.shape) != (n_heads, n, rank):
         raise KernelError("latent_attention: q_lat and out [heads, N, rank], q_rot [N, heads, rot_dim]")
@@ -1369,19 +1425,21 @@ def latent_attention(q_lat, q_rot, pool, block_table, step, out, n_heads, rank, 
     _call("attention_latent", "blm_latent_attention", _ptr(q_lat), _ptr(q_rot), _ptr(pool), _code(pool.dtype), _ptr(block_table),
           block_table.shape[1], _ptr(step.cu_seqlens), _ptr(step.slot_of_seq), _ptr(step.start_pos), _ptr(step.token_seq), _ptr(out),
           _code(out.dtype), _ptr(partial), n, step.n_seqs, step.max_q_len, n_heads, rank, rot_dim, PAGE, c_float(scale), int(n_splits),
-          _stream(), kernels=2 if n_splits > 1 else 1)
+          int(window or 0), _ptr(sink), _stream(), kernels=2 if n_splits > 1 else 1)
 
 
-def sigmoid_gate(o, gate, out):
-    """out = o * sigmoid(gate), element by element; o and out [N, C]; gate [N, C] in float32 or o's dtype, possibly a
-    column range of a wider tensor."""
+def sigmoid_gate(o, gate, out, share=1):
+    """out = o * sigmoid(gate); o and out [N, C]; gate [N, C / share] in float32 or o's dtype, possibly a column range of a
+    wider tensor: a number for every `share` neighbouring columns of o (1: element by element; a head's value size: a gate
+    per head)."""
     _need_cuda(o, out)
     if not gate.is_cuda or gate.dim() != 2 or gate.stride(1) != 1:
-        raise KernelError("sigmoid_gate: the gate is a CUDA tensor [N, C] with unit stride along its rows")
-    if o.dim() != 2 or o.shape != gate.shape or o.shape != out.shape or o.dtype != out.dtype:
-        raise KernelError("sigmoid_gate: o, gate and out [N, C]; out in o's dtype")
+        raise KernelError("sigmoid_gate: the gate is a CUDA tensor [N, C / share] with unit stride along its rows")
+    if (o.dim() != 2 or share < 1 or o.shape[1] % share or tuple(gate.shape) != (o.shape[0], o.shape[1] // share) or o.shape != out.shape
+            or o.dtype != out.dtype):
+        raise KernelError("sigmoid_gate: o and out [N, C], gate [N, C / share]; out in o's dtype")
     _call("attention_latent", "blm_sigmoid_gate", _ptr(o), _code(o.dtype), _ptr(gate), _code(gate.dtype), c_longlong(gate.stride(0)),
-          _ptr(out), o.shape[0], o.shape[1], _stream())
+          _ptr(out), o.shape[0], o.shape[1], int(share), _stream())
 
 
 # ------------------------------------------------------------------------------------------------

@@ -6,7 +6,7 @@ from .norm import DynamicTanh, DynamicTanhSpec, PostNormed, PostRMSNorm, PostRMS
 from .position import Llama3Scaling, NoPosition, NoPositionSpec, Rotary, RotarySpec, rotary_inverse_frequencies
 from .attention import Attention, AttentionSpec
 from .feed_forward import BiasedMLP, BiasedMLPSpec, SwiGLU, SwiGLUSpec
-from .block import ParallelBlock, PreNormBlock, SandwichBlock
+from .block import ParallelBlock, PostNormBlock, PreNormBlock, SandwichBlock
 from .sink_attention import SinkAttention, SinkAttentionSpec
 from .moe import SigmoidMoE, SigmoidMoESpec
 from .embedding import Embedding, EmbeddingSpec, Head, HeadSpec, PairEmbedding, PairEmbeddingSpec, ScaledEmbedding, ScaledEmbeddingSpec
@@ -19,6 +19,7 @@ from .latent_attention import LatentAttention, LatentAttentionSpec
 from .hgrn2 import Hgrn2, Hgrn2Spec
 from .wkv import Wkv, WkvSpec
 from .stream import ConcatProjection, ConcatProjectionSpec
+from .normed_attention import NormedAttention, NormedAttentionSpec
 
 __all__ = ["CacheNeed", "Part", "Runtime", "StepContext", "Linear", "RMSNorm", "RMSNormSpec", "Llama3Scaling",
            "NoPosition", "NoPositionSpec", "Rotary", "RotarySpec", "rotary_inverse_frequencies", "Attention",
@@ -27,4 +28,5 @@ __all__ = ["CacheNeed", "Part", "Runtime", "StepContext", "Linear", "RMSNorm", "
            "PostNormed", "PostRMSNorm", "PostRMSNormSpec", "BiasedMLP", "BiasedMLPSpec", "SandwichBlock", "ScaledEmbedding",
            "ScaledEmbeddingSpec", "Mamba2", "Mamba2Spec", "GatedDelta", "GatedDeltaSpec", "SigmoidAttention", "SigmoidAttentionSpec",
            "ParallelMixers", "ParallelMixersSpec", "ShortConv", "ShortConvSpec", "LatentAttention", "LatentAttentionSpec", "Hgrn2",
-           "Hgrn2Spec", "Wkv", "WkvSpec", "ConcatProjection", "ConcatProjectionSpec"]
+           "Hgrn2Spec", "Wkv", "WkvSpec", "ConcatProjection", "ConcatProjectionSpec", "NormedAttention", "NormedAttentionSpec",
+           "PostNormBlock"]

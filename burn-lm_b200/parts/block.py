@@ -212,3 +212,67 @@ class FilteredPreNormBlock:
             return a
         x = self.feed_forward_norm.add_norm(resid, a)
         return self.feed_forward.forward(x, step)
+
+
+class _StreamReader:
+    """What stands where a block's first norm would: the block reads the stream itself, and the kernel that hands it
+    the stream's rows can first norm, scale and add a pending sublayer output (parts.norm.PostNormed)."""
+    takes_post_normed = True
+
+
+@register_part("block", "postnorm")
+class PostNormBlock:
+    """Norms behind the sublayers only: x <- x + post1(mixer(x)), then x <- x + post2(feed_forward(x)).  Both sublayers
+    read the stream itself, not a normed copy; what they return is RMS-normed (norm kind "rms_post") before it joins the
+    stream.  A layer may have no feed-forward.  The norm behind a sublayer is not run by itself: its input travels as a
+    pending output to whoever reads the stream next, whose kernel norms it, adds it (fp32) and hands the sum on: here the
+    kernel that gives the next sublayer its rows in the compute dtype (in the 32-bit path the sublayer reads the stream's
+    own rows), else the next block's first norm or the model's last."""
+    family = "block"
+    graph_safe = True
+    kernel_modules = ("stream_ops",)
+
+    NAMES = ("mixer", "mixer_post_norm", "feed_forward", "feed_forward_post_norm")
+
+    def __init__(self, parts: dict):
+        if not set(self.NAMES[:2]) <= set(parts) <= set(self.NAMES) or len(parts) not in (2, 4):
+            raise ValueError(f"the postnorm block arranges parts named {self.NAMES} (the last two may be absent); the layer has {sorted(parts)}")
+        self.mixer, self.mixer_post = parts["mixer"], parts["mixer_post_norm"]
+        self.ff, self.ff_post = parts.get("feed_forward"), parts.get("feed_forward_post_norm")
+        self.reader = _StreamReader()
+
+    def first_norm(self):
+        return self.reader
+
+    def _read(self, resid, delta):
+        """The stream's rows for a sublayer, after `delta` (None, a plain output, or a pending normed one) has joined them."""
+        import torch
+
+        from .norm import PostNormed, PostRMSNorm
+        dtype = self.mixer.runtime.dtype
+        if isinstance(delta, PostNormed):
+            if dtype == torch.float32:
+                PostRMSNorm.add(resid, delta)
+                return resid
+            out = torch.empty(resid.shape, dtype=dtype, device=resid.device)
+            K.sandwich_norm(resid, delta.output, delta.weight, delta.mult, delta.eps, None, 0.0, out, delta_bias=delta.bias,
+                            second=delta.second)
+            return out
+        if delta is None and dtype == torch.float32:
+            return resid
+        out = torch.empty(resid.shape, dtype=dtype, device=resid.device)
+        K.pack_cols(resid, delta, out, 0)
+        return out
+
+    def forward(self, resid, delta, step, cache_view, next_norm=None):
+        if getattr(step, "handoff", None) is not None:
+            step.handoff.expect(None)          # no product of this block prepares a norm's input
+        x = self._read(resid, delta)
+        pending = SandwichBlock._pending(self.mixer_post, self.mixer.forward(x, step, cache_view))
+        if self.ff is not None:
+            x = self._read(resid, pending)
+            pending = SandwichBlock._pending(self.ff_post, self.ff.forward(x, step))
+        if getattr(next_norm, "takes_post_normed", False):
+            return pending
+        self.mixer_post.add(resid, pending)
+        return None

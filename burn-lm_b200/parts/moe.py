@@ -98,15 +98,20 @@ class RoutedMoESpec:
     renormalise: bool = True               # the chosen weights are divided by their sum + 1e-20
     clamp_limit: Optional[float] = None    # the experts' clamped unit: g = min(Wgate x, limit), u = clamp(Wup x, -limit, limit),
     clamp_alpha: float = 1.702             # y = g sigmoid(alpha g) (u + 1); None: silu(g) u
+    n_groups: int = 1                      # the experts form this many equal groups of neighbours; only experts of the
+    keep_groups: int = 1                   # `keep_groups` best groups can be chosen (a group's mark: its two largest choice scores)
+    unit: str = "gated"                    # "gated": W_down (act(W_gate x) * W_up x); "gelu" / "gelu_tanh": W_down gelu(W_up x),
+                                           # the exact (erf) form or the tanh one; such experts store no gate
 
 
 @register_part("feed_forward", "routed_moe")
 class RoutedMoE(SigmoidMoE):
     """The mixture of experts with the router's options spelled out: scores s = softmax(W_router h) over all experts (or
     sigmoids), the `top` experts of largest s (+ a stored correction that the weights do not see), weights s of the chosen,
-    optionally divided by their sum; out = sum weight_k expert_k(h), with the plain or the clamped gated unit.  Router
-    logits, scores and weights are fp32.  tensors: "router", "correction" (when the spec says so); "gate", "up", "down"
-    with {} where the expert's number stands."""
+    optionally divided by their sum; out = sum weight_k expert_k(h), with the plain or the clamped gated unit, or a unit
+    without a gate.  The choice may be limited to the experts of the best groups.  Router logits, scores and weights are
+    fp32.  tensors: "router", "correction" (when the spec says so); "gate" (gated units), "up", "down" with {} where the
+    expert's number stands."""
     roles = ("router", "correction", "gate", "up", "down")
     adds_to_stream = False
 
@@ -116,16 +121,37 @@ class RoutedMoE(SigmoidMoE):
             raise ValueError(f"scores are 'softmax' or 'sigmoid', not {spec.scores!r}")
         if not 1 <= spec.top <= spec.n_experts:
             raise ValueError(f"top {spec.top} of {spec.n_experts} experts")
+        if spec.unit not in self.UNITS:
+            raise ValueError(f"an expert's unit is one of {sorted(self.UNITS)}, not {spec.unit!r}")
+        if spec.unit != "gated" and spec.clamp_limit:
+            raise ValueError("the clamped unit is a gated one")
+        if (spec.n_groups < 1 or spec.n_experts % spec.n_groups or not 1 <= spec.keep_groups <= spec.n_groups
+                or spec.keep_groups * (spec.n_experts // spec.n_groups) < spec.top):
+            raise ValueError(f"{spec.n_experts} experts in {spec.n_groups} groups of which {spec.keep_groups} are kept, for {spec.top} chosen")
         self.shared = None
 
+    UNITS = {"gated": K.UNIT_GATED, "gelu": K.UNIT_GELU, "gelu_tanh": K.UNIT_GELU_TANH}
+
     def tensor_specs(self):
-        specs = super().tensor_specs()
+        s = self.spec
+        if s.unit == "gated":
+            specs = super().tensor_specs()
+        else:
+            specs = [TensorSpec(self.tensor_names["router"], (s.n_experts, s.hidden_size), init="normal:0.1")]
+            for u, d in zip(self._names("up"), self._names("down")):
+                specs += [TensorSpec(u, (s.expert_size, s.hidden_size)), TensorSpec(d, (s.hidden_size, s.expert_size))]
         if self.spec.correction:
             specs.insert(1, TensorSpec(self.tensor_names["correction"], (self.spec.n_experts,), init="normal:0.05"))
         return specs
 
     def bind(self, loaded):
-        super().bind(loaded)
+        if self.spec.unit == "gated":
+            super().bind(loaded)
+        else:                                  # no gate: the first product's weight holds the up rows alone
+            dt = self.runtime.dtype
+            self.router = loaded[self.tensor_names["router"]].to(torch.float32).contiguous()
+            self.gate_up = torch.stack([loaded[n].to(dt) for n in self._names("up")]).contiguous()
+            self.down = torch.stack([loaded[n].to(dt) for n in self._names("down")]).contiguous()
         self.correction = None
         if self.spec.correction:
             self.correction = loaded[self.tensor_names["correction"]].to(torch.float32).contiguous()
@@ -133,6 +159,6 @@ class RoutedMoE(SigmoidMoE):
     def forward(self, x, step):
         s = self.spec
         ids, weights = K.moe_route(x, self.router, s.top, softmax=s.scores == "softmax", correction=self.correction,
-                                   renormalise=s.renormalise)
+                                   renormalise=s.renormalise, n_groups=s.n_groups, keep_groups=s.keep_groups)
         return K.moe_experts(x, ids, weights, self.gate_up, self.down, weight_on_input=False, clamp_limit=s.clamp_limit or 0.0,
-                             clamp_alpha=s.clamp_alpha, out_dtype=torch.float32)
+                             clamp_alpha=s.clamp_alpha, out_dtype=torch.float32, unit=self.UNITS[s.unit])
