@@ -138,6 +138,37 @@ _PRESETS["ridopel_tiny"] = {
 }
 
 
+def _marinex_experts(n, top, ff, groups, keep):
+    return {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": n, "top": top, "groups": {"count": groups, "keep": keep}}}
+
+
+def _marinex_attention(heads, kv_heads, dim, vdim, rot_dims, scale, softcap, base, mlp):
+    return {"type": "attention", "mlp": mlp,
+            "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale, "softcap": softcap,
+                      "rot": {"dims": rot_dims, "base": base}}}
+
+
+def _marinex_latent(heads, dim, rot_dim, vdim, q_rank, kv_rank, window, scale, base, mlp, rot_dims=None):
+    return {"type": "latent_attention", "mlp": mlp,
+            "mixer": {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank, "scale": scale,
+                      "mask": {"size": window}, "rot": {"dims": rot_dim if rot_dims is None else rot_dims, "base": base}}}
+
+
+# a small Marinex decoder that uses every branch of the design: both kinds of mixer with and without a feed-forward,
+# several query heads a key/value head and one, values wider and narrower than the keys, some and all of a head's lanes
+# turning, a window inside a cache page and one across a page border, groups of experts of which some are left out
+_PRESETS["marinex_tiny"] = {
+    "architecture": "Marinex", "vocab": 288, "width": 96, "norm": {"eps": 1e-5},
+    "layers": [
+        _marinex_attention(4, 2, 24, 16, 12, 0.2, 15.0, 10000.0, _marinex_experts(8, 2, 48, 4, 2)),
+        _marinex_latent(4, 16, 16, 24, 48, 32, 20, 0.18, 10000.0, None),
+        _marinex_attention(6, 6, 16, 32, 16, 0.25, 8.0, 500000.0, _marinex_experts(6, 3, 32, 2, 1)),
+        _marinex_latent(2, 32, 8, 16, 24, 48, 70, 0.16, 5000.0, _marinex_experts(4, 1, 64, 1, 1)),
+        _marinex_attention(2, 1, 32, 32, 8, 0.18, 30.0, 10000.0, None),
+    ],
+}
+
+
 def preset_names() -> list:
     return sorted(_PRESETS)
 

@@ -30,7 +30,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Optional
 
-import dataclasses
+import copy
 
 import torch
 
@@ -212,7 +212,9 @@ class LatentAttention(Part):
             K.attention(q, s.n_heads * hd, pages, table, step.cu_seqlens, own, step.start_pos, out, n, step.n_seqs, step.max_q_len,
                         s.n_heads, s.n_heads, hd, s.scale, max_kv_len=step.max_kv_len)
         else:
-            K.attention_sink(q.view(n, s.n_heads * hd), dataclasses.replace(step, slot_of_seq=own), pages, table, out, s.n_heads,
+            own_step = copy.copy(step)                     # the expanded pages have a table of their own: sequence s is its row s
+            own_step.slot_of_seq = own
+            K.attention_sink(q.view(n, s.n_heads * hd), own_step, pages, table, out, s.n_heads,
                              s.n_heads, hd, hd, s.scale, s.window or NO_WINDOW, 0, sink=self.sink is not None, sink_logit=self.sink,
                              max_q_len=step.max_q_len)
         heads = out

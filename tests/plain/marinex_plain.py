@@ -214,3 +214,12 @@ def forward(cfg, w, tokens, collect=None):
         if collect is not None:
             collect.append(x.copy())
     return rms_norm(x, w["final.norm"], eps) @ w["head"].T
+
+
+def greedy(cfg, w, prompt, n):
+    """n tokens after the prompt, each the argmax of the last position's logits (the lowest index on a tie)."""
+    tokens, out = list(prompt), []
+    for _ in range(n):
+        out.append(int(np.argmax(forward(cfg, w, tokens)[-1])))
+        tokens.append(out[-1])
+    return out
