@@ -1,7 +1,7 @@
 """Decode and prefill throughput of the Llama-3.2-1B shape with random weights on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--config 1b|3b|8b]
-    python bench.py --compare fobilorn|nufolix|ridopel [--size 1b-layers|8b-layers]     (another design beside this one, see run_compare)
+    python bench.py --compare fobilorn|nufolix|ridopel|marinex [--size 1b-layers|8b-layers]     (another design beside this one, see run_compare)
 
 A "step" is one decode step of the whole batch.  The default run has the layer sizes of the 1B
 configuration (16 layers, width 2048, 32 heads on 8 kv heads of 64, inner 8192, vocabulary 128256,
@@ -641,6 +641,167 @@ def ridopel_kernels(z, pk):
     return out
 
 
+def marinex_configs(z):
+    """(llama, marinex) of one size.  The new design's layers take turns between grouped-query attention (Llama's head counts
+    and head size, half of a head's lanes turning, capped scores) and attention over a cached latent (Llama's head count,
+    half of a head's key lanes rotated, a latent of 4 heads' width, a query latent of half the width, a window of 1,024);
+    every layer has 8 experts without gates in 4 groups of which a token uses 2 from the best 2 groups, whose inner sizes
+    give a token the dense feed-forward's work (two matrices of 3/4 of the inner size where the dense one has three)."""
+    llama = compare_configs(z)["llama"]
+    hd, d, H = z["hd"], z["width"], z["heads"]
+    mlp = {"kind": "moe", "expert": {"ff": 3 * z["inner"] // (2 * z["top"])},
+           "router": {"experts": z["experts"], "top": z["top"], "groups": {"count": 4, "keep": 2}}}
+    att = {"type": "attention", "mlp": mlp,
+           "mixer": {"heads": H, "kv_heads": z["kv"], "dim": hd, "vdim": hd, "scale": hd ** -0.5, "softcap": 30.0,
+                     "rot": {"dims": hd // 2, "base": 500000.0}}}
+    lat = {"type": "latent_attention", "mlp": mlp,
+           "mixer": {"heads": H, "dim": hd // 2, "rot_dim": hd // 2, "vdim": hd, "q_rank": d // 2, "kv_rank": 4 * hd, "scale": hd ** -0.5,
+                     "mask": {"size": z["window"]}, "rot": {"dims": hd // 2, "base": 500000.0}}}
+    mar = {"architecture": "Marinex", "vocab": z["vocab"], "width": d, "norm": {"eps": 1e-6},
+           "layers": [att if i % 2 == 0 else lat for i in range(z["layers"])]}
+    return {"llama": llama, "marinex": mar}
+
+
+def marinex_kernels(z, pk):
+    """The new design's kernels alone, CUDA events, back to back, beside the like kernel of the dense decoder: attention with
+    a number per head, a cap and a sink (one 2,048-token prompt; 64 sequences of 1,088 tokens), windowed attention over the
+    latent (the same two cases), what stands between the projection and the attention, the kernel that joins a normed
+    sublayer output to the stream, and the experts without gates beside dense products of the work a token gets."""
+    import torch
+    from types import SimpleNamespace
+    from burn_lm_b200 import kernels as K
+    dev, bf = "cuda", torch.bfloat16
+    H, G, hd, d, W = z["heads"], z["kv"], z["hd"], z["width"], z["window"]
+    R, dr = 4 * hd, hd // 2
+    dk = hd - dr
+    out = {}
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    frac_bf16 = lambda flops, ms: round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)
+    frac_hbm = lambda nbytes, ms: round(nbytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4)
+
+    def step(n_seqs, new, cached):
+        seq = [s for s in range(n_seqs) for _ in range(new)]
+        pos = [cached + t for _ in range(n_seqs) for t in range(new)]
+        return SimpleNamespace(token_seq=i32(seq), token_pos=i32(pos), slot_of_seq=i32(list(range(n_seqs))),
+                               cu_seqlens=i32([new * s for s in range(n_seqs + 1)]), start_pos=i32([cached] * n_seqs),
+                               n_tokens=n_seqs * new, n_seqs=n_seqs, max_q_len=new, max_kv_len=cached + new)
+
+    temp = torch.rand(H, dtype=torch.float32, device=dev) + 0.5
+    sink = torch.randn(H, dtype=torch.float32, device=dev)
+
+    def attention_case(n_seqs, new, cached):
+        total = cached + new
+        pages_each = -(-total // K.PAGE)
+        n = n_seqs * new
+        bt = torch.arange(n_seqs * pages_each, dtype=torch.int32, device=dev).reshape(n_seqs, pages_each)
+        st = step(n_seqs, new, cached)
+        q = torch.randn((n, H * hd), dtype=bf, device=dev)
+        pool5 = torch.randn((n_seqs * pages_each, 2, G, K.PAGE, hd), dtype=bf, device=dev)
+        o = torch.empty_like(q)
+        ms_llama = _time(lambda: K.attention(q, q.shape[1], pool5, bt, st.cu_seqlens, st.slot_of_seq, st.start_pos, o, n, n_seqs, new,
+                                             H, G, hd, hd ** -0.5, window=0, n_splits=1, max_kv_len=total))
+        pool = pool5.reshape(n_seqs * pages_each, -1)
+        ms_new = _time(lambda: K.attention_sink(q, st, pool, bt, o, H, G, hd, hd, hd ** -0.5, 1 << 30, 0, sink=True, max_q_len=new,
+                                                head_scale=temp, softcap=30.0))
+        ms_plain = _time(lambda: K.attention_sink(q, st, pool, bt, o, H, G, hd, hd, hd ** -0.5, 1 << 30, 0, sink=True, max_q_len=new))
+        # over the latent, with the window: single tokens on the latent itself, portions on keys and values written out
+        tile = K.latent_attention_tile_rows(bf, H, R, dr, new)
+        tiles = (new * H + tile - 1) // tile * n_seqs
+        seen = min(total, W + new)
+        splits = max(1, min(2 * K.sm_count() // tiles, seen // (2 * K.PAGE), 32))
+        lpool = torch.randn((n_seqs * pages_each, K.PAGE, R + dr), dtype=bf, device=dev)
+        if new < 16:
+            q_lat = torch.randn((H, n, R), dtype=torch.float32, device=dev) * 0.1
+            q_rot = torch.randn((n, H, dr), dtype=torch.float32, device=dev)
+            mixed = torch.empty((H, n, R), dtype=bf, device=dev)
+            partial = torch.empty(max(1, K.latent_attention_scratch_floats(n, H, R, splits)), dtype=torch.float32, device=dev)
+            ms_lat = _time(lambda: K.latent_attention(q_lat, q_rot, lpool, bt, st, mixed, H, R, dr, hd ** -0.5, n_splits=splits,
+                                                      partial=partial if splits > 1 else None, window=W, sink=sink), reps=5)
+            return ms_llama, ms_new, ms_plain, ms_lat, total, splits
+        rows = n_seqs * pages_each * K.PAGE
+        gathered = torch.empty((rows, R + dr), dtype=bf, device=dev)
+        up = torch.randn((H * dk + H * hd, R), dtype=bf, device=dev) * R ** -0.5
+        whole = torch.empty((n_seqs * pages_each, 2, H, K.PAGE, hd), dtype=bf, device=dev)
+
+        def written_out():
+            K.latent_gather(lpool, bt, st, gathered, pages_each, R + dr, window=W)
+            kv = torch.mm(gathered[:, :R], up.t())
+            K.latent_expand(kv, gathered, whole, H, dk, dr, hd, R)
+            K.attention_sink(q, st, whole, bt, o, H, H, hd, hd, hd ** -0.5, W, 0, sink=True, sink_logit=sink, max_q_len=new)
+        return ms_llama, ms_new, ms_plain, _time(written_out), total, splits
+
+    ms_l, ms_n, ms_p, ms_lat, total, _ = attention_case(1, 2048, 0)
+    flops = 4.0 * H * hd * 2048 * 2049 / 2
+    flops_w = 4.0 * H * hd * sum(min(t + 1, W) for t in range(2048)) + 2.0 * 2048 * R * H * (dk + hd)
+    out["attention_prefill_2048"] = {"llama_ms": round(ms_l, 4), "marinex_ms": round(ms_n, 4), "marinex_without_cap_and_numbers_ms": round(ms_p, 4),
+                                     "llama_frac_bf16": frac_bf16(flops, ms_l), "marinex_frac_bf16": frac_bf16(flops, ms_n),
+                                     "marinex_latent_window_ms": round(ms_lat, 4), "marinex_latent_frac_bf16": frac_bf16(flops_w, ms_lat)}
+    ms_l, ms_n, ms_p, ms_lat, total, splits = attention_case(64, 1, 1087)
+    nbytes = 64 * G * total * 2 * hd * 2
+    lbytes = 64 * min(total, W) * (R + dr) * 2
+    out["attention_decode_b64"] = {"llama_ms": round(ms_l, 4), "marinex_ms": round(ms_n, 4), "marinex_without_cap_and_numbers_ms": round(ms_p, 4),
+                                   "keys_seen": total, "llama_frac_hbm": frac_hbm(nbytes, ms_l), "marinex_frac_hbm": frac_hbm(nbytes, ms_n),
+                                   "marinex_latent_window_ms": round(ms_lat, 4), "latent_keys_seen": min(total, W), "latent_key_shares": splits,
+                                   "marinex_latent_frac_hbm": frac_hbm(lbytes, ms_lat)}
+    # between the projection and the attention: norms over heads, the turn, unit values and the append, beside the dense
+    # decoder's turn and append; and the kernel that joins a normed output to the stream beside the dense decoder's add + norm
+    for n_seqs, new, cached in ((1, 2048, 0), (64, 1, 1087)):
+        st = step(n_seqs, new, cached)
+        n = st.n_tokens
+        pages_each = -(-(cached + new) // K.PAGE)
+        bt = torch.arange(n_seqs * pages_each, dtype=torch.int32, device=dev).reshape(n_seqs, pages_each)
+        cols = (H + 2 * G) * hd
+        proj = torch.randn((n, cols), dtype=torch.float32, device=dev)
+        qkv = torch.randn((n, cols), dtype=bf, device=dev)
+        pool5 = torch.empty((n_seqs * pages_each, 2, G, K.PAGE, hd), dtype=bf, device=dev)
+        q = torch.empty((n, H * hd), dtype=bf, device=dev)
+        wq = torch.ones(hd, dtype=torch.float32, device=dev)
+        freq = torch.tensor([500000.0 ** (-2.0 * i / (hd // 2)) for i in range(hd // 4)], dtype=torch.float64, device=dev)
+        freq_l = torch.tensor([500000.0 ** (-2.0 * i / hd) for i in range(hd // 2)], dtype=torch.float64, device=dev)
+        ms_new = _time(lambda: K.head_norm_rope_append(proj, st, pool5.view(n_seqs * pages_each, -1), bt, q, H, G, hd, hd, q_weight=wq, k_weight=wq,
+                                                       eps=1e-6, value_norm=True, freq=freq, rotary_dims=hd // 2))
+        ms_llama = _time(lambda: K.rope_append(qkv, st.token_seq, st.token_pos, st.slot_of_seq, bt, freq_l, hd, K.PAIRS_HALVES, pool5, H, G, hd,
+                                               write_cache=True, max_position=cached + new - 1))
+        resid = torch.randn((n, d), dtype=torch.float32, device=dev)
+        delta = torch.randn((n, d), dtype=torch.float32, device=dev)
+        gamma = torch.ones(d, dtype=torch.float32, device=dev)
+        x = torch.empty((n, d), dtype=bf, device=dev)
+        ms_join = _time(lambda: K.sandwich_norm(resid, delta, gamma, 1.0, 1e-6, None, 0.0, x))
+        ms_norm = _time(lambda: K.add_rmsnorm(resid, delta, gamma.to(bf), 1e-6, x))
+        out[f"between_{n_seqs}x{new}"] = {"marinex_norms_turn_append_ms": round(ms_new, 4), "llama_turn_append_ms": round(ms_llama, 4),
+                                          "marinex_frac_hbm": frac_hbm(n * cols * 6.0, ms_new), "llama_frac_hbm": frac_hbm(n * cols * 4.0, ms_llama),
+                                          "marinex_join_stream_ms": round(ms_join, 4), "llama_add_norm_ms": round(ms_norm, 4),
+                                          "marinex_join_frac_hbm": frac_hbm(n * d * 14.0, ms_join), "llama_add_norm_frac_hbm": frac_hbm(n * d * 14.0, ms_norm)}
+    # feed-forward: a token's experts without gates beside dense products of the same work
+    E, top = z["experts"], z["top"]
+    each = 3 * z["inner"] // (2 * top)
+    up = torch.randn((E, each, d), dtype=bf, device=dev) * 0.02
+    down = torch.randn((E, d, each), dtype=bf, device=dev) * 0.02
+    router = torch.randn((E, d), dtype=torch.float32, device=dev)
+    correction = torch.randn(E, dtype=torch.float32, device=dev) * 0.05
+    w1 = torch.randn((2 * z["inner"], d), dtype=bf, device=dev) * 0.02
+    w2 = torch.randn((d, z["inner"]), dtype=bf, device=dev) * 0.02
+    for n in (2048, 64):
+        h = torch.randn((n, d), dtype=bf, device=dev)
+        ms_route = _time(lambda: K.moe_route(h, router, top, correction=correction, n_groups=4, keep_groups=2))
+        ids, weights = K.moe_route(h, router, top, correction=correction, n_groups=4, keep_groups=2)
+        ms_moe = _time(lambda: K.moe_experts(h, ids, weights, up, down, weight_on_input=False, out_dtype=torch.float32, unit=K.UNIT_GELU))
+        a = torch.empty((n, z["inner"]), dtype=bf, device=dev)
+
+        def dense():
+            gu = torch.mm(h, w1.t())
+            K.swiglu(gu, a)
+            return torch.mm(a, w2.t())
+        ms_dense = _time(dense)
+        flops = 2.0 * n * top * 2 * each * d
+        wbytes = 2.0 * 2 * each * d * min(E, n * top)
+        out[f"experts_{n}_tokens"] = {
+            "route_ms": round(ms_route, 4), "marinex_ms": round(ms_moe, 4), "dense_same_work_ms": round(ms_dense, 4),
+            "marinex_frac_bf16": frac_bf16(flops, ms_moe), "dense_frac_bf16": frac_bf16(flops, ms_dense),
+            "marinex_frac_hbm": frac_hbm(wbytes, ms_moe), "dense_frac_hbm": frac_hbm(2.0 * 3 * z["inner"] * d, ms_dense)}
+    return out
+
+
 def run_compare(args):
     """One JSON line per size and model: prefill of one 2,048-token prompt and decode at batch 8 and 64 after 512-token
     prompts, for the dense Llama decoder and the named design (Fobilorn with dense feed-forwards and with experts, Nufolix,
@@ -654,9 +815,9 @@ def run_compare(args):
     for size, z in COMPARE_SIZES.items():
         if args.size and size != args.size:
             continue
-        if args.compare == "ridopel":
+        if args.compare in ("ridopel", "marinex"):
             z = dict(z, experts=8)          # 8 experts of half the dense inner size each: four times the dense layer's weights
-        configs = {"nufolix": nufolix_configs, "ridopel": ridopel_configs}.get(args.compare, compare_configs)(z)
+        configs = {"nufolix": nufolix_configs, "ridopel": ridopel_configs, "marinex": marinex_configs}.get(args.compare, compare_configs)(z)
         for name, cfg in configs.items():
             vocab = z["vocab"]
             lm = blm.load_random(cfg, seed=0, dtype="bfloat16", max_seq_len=4096, max_batch=64, max_tokens=64 * 1024)
@@ -673,7 +834,7 @@ def run_compare(args):
             print(json.dumps(line), flush=True)
             del lm, engine
             torch.cuda.empty_cache()
-        alone = {"nufolix": nufolix_kernels, "ridopel": ridopel_kernels}.get(args.compare, compare_kernels)(z, pk)
+        alone = {"nufolix": nufolix_kernels, "ridopel": ridopel_kernels, "marinex": marinex_kernels}.get(args.compare, compare_kernels)(z, pk)
         print(json.dumps({"compare": size, "kernels": alone, "peaks": pk["source"]}), flush=True)
     return 0
 
@@ -788,7 +949,7 @@ def main():
     ap.add_argument("--only", default=None, choices=["decode", "prefill", "sweep"],
                     help="run one workload briefly (for profilers), or a sweep over batch sizes and context lengths")
     ap.add_argument("--prompt-tokens", type=int, default=0, help="with --only prefill: one prompt of this many tokens instead of the workload's")
-    ap.add_argument("--compare", default=None, choices=["fobilorn", "nufolix", "ridopel"],
+    ap.add_argument("--compare", default=None, choices=["fobilorn", "nufolix", "ridopel", "marinex"],
                     help="instead of the workload: the named design beside the dense Llama decoder at equal layer sizes "
                          "(prefill and decode throughput, then its kernels alone), one JSON line each")
     ap.add_argument("--size", default=None, choices=sorted(COMPARE_SIZES), help="with --compare: one of the sizes only")

@@ -240,6 +240,15 @@ struct ScoreOpts {
     float cap;                   // > 0: s <- cap tanh(s / cap)
 };
 __device__ __forceinline__ float capped(float s, float cap) { return cap > 0.f ? cap * tanhf(s / cap) : s; }
+// The same for the tensor-core kernels, whose operands are bfloat16: tanh(x) = (1 - e) / (1 + e), e = exp(-2 |x|), by the
+// special function unit (relative error about 1e-6, far below what the operands' rounding leaves in a score); the library's
+// tanhf doubled those kernels' time.
+__device__ __forceinline__ float capped_fast(float s, float cap, float inv_cap) {
+    if (!(cap > 0.f)) return s;
+    const float x = s * inv_cap;
+    const float e = __expf(-2.0f * fabsf(x));
+    return copysignf(cap * __fdividef(1.0f - e, 1.0f + e), x);
+}
 
 template <typename T>
 __global__ void attention_sink_rows_kernel(const T* __restrict__ q, const T* __restrict__ pool, long long page_elems,
@@ -603,6 +612,7 @@ __global__ void __launch_bounds__(128 * HB) attention_sink_prompt_kernel(
     const float pre = scale * (so.head_scale ? so.head_scale[head] : 1.f);
     const bool shaped = so.cap > 0.f || !(pre > 0.f);
     const float scale2 = (shaped ? 1.f : pre) * 1.4426950408889634f;
+    const float inv_cap = so.cap > 0.f ? 1.0f / so.cap : 0.f;
     float m[2], l[2], o[NV][4];
     m[0] = m[1] = sink ? (so.sink_logit ? so.sink_logit[head] * 1.4426950408889634f : 0.f) : -INFINITY;
     l[0] = l[1] = sink ? 0.25f : 0.f;                  // a quad's four lanes add up to the sink's one
@@ -637,7 +647,7 @@ __global__ void __launch_bounds__(128 * HB) attention_sink_prompt_kernel(
 #pragma unroll
             for (int j = 0; j < 8; ++j)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) s[j][e] = capped(s[j][e] * pre, so.cap);
+                for (int e = 0; e < 4; ++e) s[j][e] = capped_fast(s[j][e] * pre, so.cap, inv_cap);
         }
         float mx0 = -INFINITY, mx1 = -INFINITY;
         // every row of this warp sees every key of the page when the page lies behind the warp's first row and inside
@@ -809,6 +819,7 @@ __global__ void __launch_bounds__(128) attention_sink_decode_kernel(
     const bool with_sink = sink && split == 0 && warp == 0;      // the sink is counted once
     const float log2e = 1.4426950408889634f;                     // scores in units of log 2: the exponentials are exp2
     float m[2], l[2], o[NV][4], pre[2];
+    const float inv_cap = so.cap > 0.f ? 1.0f / so.cap : 0.f;
 #pragma unroll
     for (int half = 0; half < 2; ++half) {                       // this thread's two rows are two heads of the group
         const int r = quad + 8 * half;
@@ -846,7 +857,7 @@ __global__ void __launch_bounds__(128) attention_sink_decode_kernel(
             for (int e = 0; e < 4; ++e) {
                 const int key = pg * kTileK + 16 * warp + 8 * j + pair + (e & 1);
                 const bool sees = key <= pos && (pos - key < window || key < keep_first);
-                s[j][e] = sees ? capped(s[j][e] * pre[e >> 1], so.cap) * log2e : -INFINITY;
+                s[j][e] = sees ? capped_fast(s[j][e] * pre[e >> 1], so.cap, inv_cap) * log2e : -INFINITY;
             }
         float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
         float mx1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
