@@ -26,7 +26,7 @@ template <typename T>
 __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router, int width, int n_experts, int top,
                                  int* __restrict__ ids, float* __restrict__ weights, int softmax, const float* __restrict__ correction,
                                  int renorm, int n_groups, int keep_groups) {
-    extern __shared__ float smem[];
+    extern __shared__ __align__(16) float smem[];
     float* x = smem;                     // [width]
     float* score = smem + width;         // [n_experts]: what a chosen expert is weighted by
     float* choice = score + n_experts;   // [n_experts]: what the choice looks at (the score, plus the correction)
@@ -38,7 +38,19 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
     for (int e = warp; e < n_experts; e += n_warps) {
         const float* w = router + (size_t)e * width;
         float z = 0.f;
-        for (int d = lane; d < width; d += 32) z = fmaf(w[d], x[d], z);
+        if ((width & 127) == 0) {            // four loads of 16 bytes on their way at once, four sums: the loop waits for memory, not for itself
+            const float4* w4 = reinterpret_cast<const float4*>(w);
+            const float4* x4 = reinterpret_cast<const float4*>(x);
+            float z0 = 0.f, z1 = 0.f, z2 = 0.f, z3 = 0.f;
+#pragma unroll 4
+            for (int d = lane; d < width / 4; d += 32) {
+                const float4 a = __ldg(w4 + d), c = x4[d];
+                z0 = fmaf(a.x, c.x, z0); z1 = fmaf(a.y, c.y, z1); z2 = fmaf(a.z, c.z, z2); z3 = fmaf(a.w, c.w, z3);
+            }
+            z = (z0 + z1) + (z2 + z3);
+        } else {
+            for (int d = lane; d < width; d += 32) z = fmaf(w[d], x[d], z);
+        }
         z = warp_sum(z);
         // (a row of no sequence may hold anything, a NaN too: its score is 0, so that it still names experts that exist)
         if (lane == 0) score[e] = softmax ? (z == z ? z : 0.f) : (z == z ? 1.0f / (1.0f + expf(-z)) : 0.f);
@@ -333,7 +345,10 @@ __global__ void moe_down_kernel(const T* __restrict__ act, const int* __restrict
 // buffers in turn; four warps, each 16 places of the tile.  Width and inner size are multiples of 8 (16-byte copies).
 // A weight on the expert's input is applied to both products' sums instead, W (s x) = s (W x), in fp32.
 // ---------------------------------------------------------------------------------------------
-constexpr int kTM = 64, kTN = 64, kTK = 64, kTStride = kTK + 8;     // rows 16 bytes apart modulo 128: ldmatrix reads eight at once
+#ifndef BLM_MOE_TK
+#define BLM_MOE_TK 64
+#endif
+constexpr int kTM = 64, kTN = 64, kTK = BLM_MOE_TK, kTStride = kTK + 8;     // rows 16 bytes apart modulo 128: ldmatrix reads eight at once
 constexpr int kTile = kTM * kTStride;                               // elements of one staged operand
 
 __device__ __forceinline__ void moe_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -351,7 +366,16 @@ __device__ __forceinline__ void moe_cp16(__nv_bfloat16* dst, const __nv_bfloat16
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void moe_cp_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
-__device__ __forceinline__ void moe_cp_wait_all_but_one() { asm volatile("cp.async.wait_group 1;\n" ::: "memory"); }
+template <int N> __device__ __forceinline__ void moe_cp_wait_all_but() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+// Slices of the reduction in shared memory at once: one worked on, the others on their way.  Measured with 8 experts of
+// 6,144 x 2,048 (10,752 x 4,096) without gates, 2 chosen: two slices of 64 lanes 198 / 215 / 1,110 us for 8 / 64 / 2,048 tokens
+// (450 / 574 / 3,664); three slices 196 / 221 / 1,144 (453 / 535 / 3,780); four 196 / 219 / 1,213 (554 / 621 / 4,007); two
+// slices of 128 lanes (-DBLM_MOE_TK=128) 166 / 208 / 1,157 (363 / 563 / 3,811); of 256 lanes 230 / 277 / 1,963.  So two
+// slices of 64 it stays: more copies in flight do not help, longer pieces of a weight row help the fewest tokens only.
+#ifndef BLM_MOE_STAGES
+#define BLM_MOE_STAGES 2
+#endif
+constexpr int kMoeStages = BLM_MOE_STAGES;
 
 // rows [c0, c0 + 64) x lanes [k0, k0 + 64) of a weight [n_rows, n_cols] into ws[64][kTStride]; zeros outside
 __device__ __forceinline__ void moe_stage_weight(__nv_bfloat16* ws, const __nv_bfloat16* __restrict__ w, int n_rows, int n_cols, int c0, int k0) {
@@ -401,7 +425,8 @@ __global__ void __launch_bounds__(128) moe_gate_up_tc_kernel(const __nv_bfloat16
                                                              const __nv_bfloat16* __restrict__ w_gu, __nv_bfloat16* __restrict__ act,
                                                              int width, int ff, int n_experts, int top, int scale_input, GluAct glu) {
     extern __shared__ __align__(16) unsigned char moe_smem[];
-    __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(moe_smem);      // 2 x (x, gate, up)
+    __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(moe_smem);      // kMoeStages x (x, gate, up); without a gate: (x, up)
+    constexpr int kOperands = kGated ? 3 : 2;
     __shared__ int token_of[kTM];
     __shared__ float scale_of[kTM];
     int e, first, last;
@@ -425,7 +450,7 @@ __global__ void __launch_bounds__(128) moe_gate_up_tc_kernel(const __nv_bfloat16
     const __nv_bfloat16* wg = w_gu + (size_t)e * (kGated ? 2 : 1) * ff * width;
     const __nv_bfloat16* wu = wg + (size_t)ff * width;
     auto stage_slice = [&](int buf, int k0) {
-        __nv_bfloat16* xs = stage + buf * 3 * kTile;
+        __nv_bfloat16* xs = stage + buf * kOperands * kTile;
         for (int idx = threadIdx.x; idx < kTM * (kTK / 8); idx += blockDim.x) {
             const int r = idx / (kTK / 8), kk = (idx % (kTK / 8)) * 8;
             const int tok = token_of[r];
@@ -441,16 +466,19 @@ __global__ void __launch_bounds__(128) moe_gate_up_tc_kernel(const __nv_bfloat16
     const int a_off = (warp * 16 + lrow + (lmat & 1) * 8) * kTStride + (lmat >> 1) * 8;
     const int b_off = (lrow + (lmat >> 1) * 8) * kTStride + (lmat & 1) * 8;
     const unsigned stage_at = (unsigned)__cvta_generic_to_shared(stage);
-    stage_slice(0, 0);
-    moe_cp_commit();
     const int n_slices = (width + kTK - 1) / kTK;
-    for (int it = 0; it < n_slices; ++it) {
-        const int buf = it & 1;
-        if (it + 1 < n_slices) stage_slice(buf ^ 1, (it + 1) * kTK);
+#pragma unroll
+    for (int ahead = 0; ahead < kMoeStages - 1; ++ahead) {
+        if (ahead < n_slices) stage_slice(ahead, ahead * kTK);
         moe_cp_commit();
-        moe_cp_wait_all_but_one();
+    }
+    for (int it = 0; it < n_slices; ++it) {
+        const int buf = it % kMoeStages;
+        if (it + kMoeStages - 1 < n_slices) stage_slice((it + kMoeStages - 1) % kMoeStages, (it + kMoeStages - 1) * kTK);   // where the slice before this one lay
+        moe_cp_commit();
+        moe_cp_wait_all_but<kMoeStages - 1>();
         __syncthreads();
-        const unsigned xs = stage_at + buf * 3 * kTile * 2;
+        const unsigned xs = stage_at + buf * kOperands * kTile * 2;
         if (kGated) moe_warp_product2(g, u, xs + a_off * 2, xs + (kTile + b_off) * 2, xs + (2 * kTile + b_off) * 2);
         else moe_warp_product(g, xs + a_off * 2, xs + (kTile + b_off) * 2);
         __syncthreads();
@@ -480,7 +508,7 @@ __global__ void __launch_bounds__(128) moe_down_tc_kernel(const __nv_bfloat16* _
                                                           const __nv_bfloat16* __restrict__ w_down, float* __restrict__ y, int width, int ff,
                                                           int n_experts) {
     extern __shared__ __align__(16) unsigned char moe_smem[];
-    __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(moe_smem);      // 2 x (x, weight)
+    __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(moe_smem);      // kMoeStages x (x, weight)
     int e, first, last;
     if (!moe_find_tile(offsets, n_experts, blockIdx.x, &e, &first, &last, kTM)) return;
     const int c0 = blockIdx.y * kTN;
@@ -502,14 +530,17 @@ __global__ void __launch_bounds__(128) moe_down_tc_kernel(const __nv_bfloat16* _
     const int a_off = (warp * 16 + lrow + (lmat & 1) * 8) * kTStride + (lmat >> 1) * 8;
     const int b_off = (lrow + (lmat >> 1) * 8) * kTStride + (lmat & 1) * 8;
     const unsigned stage_at = (unsigned)__cvta_generic_to_shared(stage);
-    stage_slice(0, 0);
-    moe_cp_commit();
     const int n_slices = (ff + kTK - 1) / kTK;
-    for (int it = 0; it < n_slices; ++it) {
-        const int buf = it & 1;
-        if (it + 1 < n_slices) stage_slice(buf ^ 1, (it + 1) * kTK);
+#pragma unroll
+    for (int ahead = 0; ahead < kMoeStages - 1; ++ahead) {
+        if (ahead < n_slices) stage_slice(ahead, ahead * kTK);
         moe_cp_commit();
-        moe_cp_wait_all_but_one();
+    }
+    for (int it = 0; it < n_slices; ++it) {
+        const int buf = it % kMoeStages;
+        if (it + kMoeStages - 1 < n_slices) stage_slice((it + kMoeStages - 1) % kMoeStages, (it + kMoeStages - 1) * kTK);
+        moe_cp_commit();
+        moe_cp_wait_all_but<kMoeStages - 1>();
         __syncthreads();
         const unsigned xs = stage_at + buf * 2 * kTile * 2;
         moe_warp_product(acc, xs + a_off * 2, xs + (kTile + b_off) * 2);
@@ -526,9 +557,201 @@ __global__ void __launch_bounds__(128) moe_down_tc_kernel(const __nv_bfloat16* _
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same products for steps that bring an expert a few tokens only (single-token steps of a batch): tiles of 16 places x
+// 64 outputs, the four warps of a block 16 outputs each, the reduction in slices of 128 lanes (longer pieces of a weight
+// row a copy).  With tiles of 64 places three warps in four multiplied rows of zeros, and the blocks were bound by the
+// instructions they issued, not by the weights they stream.  The second product has few output tiles (width / 64 a
+// tile of places), so its reduction is cut over gridDim.z blocks, each of which leaves its share of the sums in a plane of
+// its own ([splits][places][width]); the kernel that sums a token's experts adds the planes in order.
+// ---------------------------------------------------------------------------------------------
+constexpr int kSM = 16, kSN = 64, kSK = 128, kSStride = kSK + 8;
+constexpr int kSTileX = kSM * kSStride, kSTileW = kSN * kSStride;
+#ifndef BLM_MOE_SKINNY_PAIRS
+#define BLM_MOE_SKINNY_PAIRS 32      // up to this many (token, expert) pairs an expert on average the skinny kernels run
+#endif
+
+__device__ __forceinline__ void moe_stage_weight_skinny(__nv_bfloat16* ws, const __nv_bfloat16* __restrict__ w, int n_rows, int n_cols, int c0,
+                                                        int k0, int k_end) {
+    for (int idx = threadIdx.x; idx < kSN * (kSK / 8); idx += blockDim.x) {
+        const int r = idx / (kSK / 8), kk = (idx % (kSK / 8)) * 8;
+        const bool in = c0 + r < n_rows && k0 + kk < k_end;
+        moe_cp16(ws + r * kSStride + kk, in ? w + (size_t)(c0 + r) * n_cols + k0 + kk : w, in);
+    }
+}
+
+template <bool kGated>
+__global__ void __launch_bounds__(128) moe_up_skinny_kernel(const __nv_bfloat16* __restrict__ h, const float* __restrict__ weights,
+                                                            const int* __restrict__ order, const int* __restrict__ offsets,
+                                                            const __nv_bfloat16* __restrict__ w_gu, __nv_bfloat16* __restrict__ act,
+                                                            int width, int ff, int n_experts, int top, int scale_input, GluAct glu) {
+    extern __shared__ __align__(16) unsigned char moe_smem[];
+    __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(moe_smem);      // 2 x (x, gate, up); without a gate: (x, up)
+    constexpr int kStage = kSTileX + (kGated ? 2 : 1) * kSTileW;
+    __shared__ int token_of[kSM];
+    __shared__ float scale_of[kSM];
+    int e, first, last;
+    if (!moe_find_tile(offsets, n_experts, blockIdx.x, &e, &first, &last, kSM)) return;
+    const int c0 = blockIdx.y * kSN;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, quad = lane >> 2, pair = (lane & 3) * 2;
+    const int lrow = lane & 7, lmat = lane >> 3;
+    if (threadIdx.x < kSM) {
+        const int place = first + threadIdx.x;
+        int tok = -1;
+        float sc = 1.f;
+        if (place < last) {
+            const int p = order[place];
+            tok = p / top;
+            if (scale_input) sc = weights[p];
+        }
+        token_of[threadIdx.x] = tok;
+        scale_of[threadIdx.x] = sc;
+    }
+    __syncthreads();
+    const __nv_bfloat16* wg = w_gu + (size_t)e * (kGated ? 2 : 1) * ff * width;
+    const __nv_bfloat16* wu = wg + (size_t)ff * width;
+    auto stage_slice = [&](int buf, int k0) {
+        __nv_bfloat16* xs = stage + buf * kStage;
+        for (int idx = threadIdx.x; idx < kSM * (kSK / 8); idx += blockDim.x) {
+            const int r = idx / (kSK / 8), kk = (idx % (kSK / 8)) * 8;
+            const int tok = token_of[r];
+            const bool in = tok >= 0 && k0 + kk < width;
+            moe_cp16(xs + r * kSStride + kk, in ? h + (size_t)tok * width + k0 + kk : h, in);
+        }
+        moe_stage_weight_skinny(xs + kSTileX, wg, ff, width, c0, k0, width);
+        if (kGated) moe_stage_weight_skinny(xs + kSTileX + kSTileW, wu, ff, width, c0, k0, width);
+    };
+    float g[2][4], u[2][4];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) g[j][0] = g[j][1] = g[j][2] = g[j][3] = u[j][0] = u[j][1] = u[j][2] = u[j][3] = 0.f;
+    const int a_off = (lrow + (lmat & 1) * 8) * kSStride + (lmat >> 1) * 8;
+    const int b_off = (warp * 16 + lrow + (lmat >> 1) * 8) * kSStride + (lmat & 1) * 8;
+    const unsigned stage_at = (unsigned)__cvta_generic_to_shared(stage);
+    stage_slice(0, 0);
+    moe_cp_commit();
+    const int n_slices = (width + kSK - 1) / kSK;
+    for (int it = 0; it < n_slices; ++it) {
+        const int buf = it & 1;
+        if (it + 1 < n_slices) stage_slice(buf ^ 1, (it + 1) * kSK);
+        moe_cp_commit();
+        moe_cp_wait_all_but<1>();
+        __syncthreads();
+        const unsigned xs = stage_at + buf * kStage * 2;
+#pragma unroll
+        for (int kk = 0; kk < kSK; kk += 16) {
+            uint32_t a[4], b[4];
+            moe_ldsm_x4(a, xs + (a_off + kk) * 2);
+            moe_ldsm_x4(b, xs + (kSTileX + b_off + kk) * 2);
+            moe_mma(g[0], a, b[0], b[1]);
+            moe_mma(g[1], a, b[2], b[3]);
+            if (kGated) {
+                moe_ldsm_x4(b, xs + (kSTileX + kSTileW + b_off + kk) * 2);
+                moe_mma(u[0], a, b[0], b[1]);
+                moe_mma(u[1], a, b[2], b[3]);
+            }
+        }
+        __syncthreads();
+    }
+    const int p0 = first + quad, p1 = p0 + 8;
+    const float s0 = scale_of[quad], s1 = scale_of[quad + 8];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const int c = c0 + warp * 16 + 8 * j + pair;
+        if (c < ff) {                                   // ff is even: c + 1 < ff as well
+            if (p0 < last)
+                *reinterpret_cast<__nv_bfloat162*>(act + (size_t)p0 * ff + c) =
+                    __floats2bfloat162_rn(glu_act(s0 * g[j][0], s0 * u[j][0], glu), glu_act(s0 * g[j][1], s0 * u[j][1], glu));
+            if (p1 < last)
+                *reinterpret_cast<__nv_bfloat162*>(act + (size_t)p1 * ff + c) =
+                    __floats2bfloat162_rn(glu_act(s1 * g[j][2], s1 * u[j][2], glu), glu_act(s1 * g[j][3], s1 * u[j][3], glu));
+        }
+    }
+}
+
+// y[z][place, c] = sum over the z-th share of k of act[place, k] Wdown[e, c, k]
+__global__ void __launch_bounds__(128) moe_down_skinny_kernel(const __nv_bfloat16* __restrict__ act, const int* __restrict__ offsets,
+                                                              const __nv_bfloat16* __restrict__ w_down, float* __restrict__ y, int width, int ff,
+                                                              int n_experts, long long plane) {
+    extern __shared__ __align__(16) unsigned char moe_smem[];
+    __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(moe_smem);      // 2 x (x, weight)
+    constexpr int kStage = kSTileX + kSTileW;
+    int e, first, last;
+    if (!moe_find_tile(offsets, n_experts, blockIdx.x, &e, &first, &last, kSM)) return;
+    const int c0 = blockIdx.y * kSN;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, quad = lane >> 2, pair = (lane & 3) * 2;
+    const int lrow = lane & 7, lmat = lane >> 3;
+    const int slices_all = (ff + kSK - 1) / kSK, per = (slices_all + (int)gridDim.z - 1) / (int)gridDim.z;
+    const int k_begin = min(ff, (int)blockIdx.z * per * kSK), k_end = min(ff, ((int)blockIdx.z + 1) * per * kSK);
+    const __nv_bfloat16* wd = w_down + (size_t)e * width * ff;
+    auto stage_slice = [&](int buf, int k0) {
+        __nv_bfloat16* xs = stage + buf * kStage;
+        for (int idx = threadIdx.x; idx < kSM * (kSK / 8); idx += blockDim.x) {
+            const int r = idx / (kSK / 8), kk = (idx % (kSK / 8)) * 8;
+            const bool in = first + r < last && k0 + kk < k_end;
+            moe_cp16(xs + r * kSStride + kk, in ? act + (size_t)(first + r) * ff + k0 + kk : act, in);
+        }
+        moe_stage_weight_skinny(xs + kSTileX, wd, width, ff, c0, k0, k_end);
+    };
+    float acc[2][4];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    const int a_off = (lrow + (lmat & 1) * 8) * kSStride + (lmat >> 1) * 8;
+    const int b_off = (warp * 16 + lrow + (lmat >> 1) * 8) * kSStride + (lmat & 1) * 8;
+    const unsigned stage_at = (unsigned)__cvta_generic_to_shared(stage);
+    const int n_slices = (k_end - k_begin + kSK - 1) / kSK;
+    if (n_slices > 0) stage_slice(0, k_begin);
+    moe_cp_commit();
+    for (int it = 0; it < n_slices; ++it) {
+        const int buf = it & 1;
+        if (it + 1 < n_slices) stage_slice(buf ^ 1, k_begin + (it + 1) * kSK);
+        moe_cp_commit();
+        moe_cp_wait_all_but<1>();
+        __syncthreads();
+        const unsigned xs = stage_at + buf * kStage * 2;
+#pragma unroll
+        for (int kk = 0; kk < kSK; kk += 16) {
+            uint32_t a[4], b[4];
+            moe_ldsm_x4(a, xs + (a_off + kk) * 2);
+            moe_ldsm_x4(b, xs + (kSTileX + b_off + kk) * 2);
+            moe_mma(acc[0], a, b[0], b[1]);
+            moe_mma(acc[1], a, b[2], b[3]);
+        }
+        __syncthreads();
+    }
+    float* out = y + (size_t)blockIdx.z * plane;
+    const int p0 = first + quad, p1 = p0 + 8;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const int c = c0 + warp * 16 + 8 * j + pair;
+        if (c < width) {                                // width is even
+            if (p0 < last) *reinterpret_cast<float2*>(out + (size_t)p0 * width + c) = make_float2(acc[j][0], acc[j][1]);
+            if (p1 < last) *reinterpret_cast<float2*>(out + (size_t)p1 * width + c) = make_float2(acc[j][2], acc[j][3]);
+        }
+    }
+}
+
+static bool moe_runs_skinny(int dtype, long long pairs, int width, int ff, int n_experts) {
+    return dtype == BLM_BF16 && width % 8 == 0 && ff % 8 == 0 && pairs <= (long long)BLM_MOE_SKINNY_PAIRS * n_experts;
+}
+
+// Over how many blocks the second product's reduction is cut (the planes of y the caller provides): 1 unless the skinny
+// kernels run and their tiles of places x output tiles would leave most multiprocessors without a block.
+BLM_API int blm_moe_down_splits(int dtype, int n_tokens, int width, int ff, int n_experts, int top) {
+    const long long pairs = (long long)n_tokens * top;
+    if (!moe_runs_skinny(dtype, pairs, width, ff, n_experts)) return 1;
+    const long long busy = (pairs < n_experts ? pairs : n_experts) + pairs / kSM;      // tiles of places that have a place
+    const long long blocks = busy * ((width + kSN - 1) / kSN);
+    long long splits = (4 * 148 + blocks - 1) / blocks;
+    const long long most = (ff + 4 * kSK - 1) / (4 * kSK);                             // four slices a block at least
+    if (splits > most) splits = most;
+    if (splits > 16) splits = 16;
+    return splits < 1 ? 1 : (int)splits;
+}
+
 BLM_API int blm_moe_experts(const void* h, int dtype, const float* weights, const int* order, const int* offsets, const void* w_gu,
                             const void* w_down, void* act, float* y, int n_tokens, int width, int ff, int n_experts, int top,
-                            int scale_input, float act_limit, float act_alpha, int plain_unit, cudaStream_t stream) {
+                            int scale_input, float act_limit, float act_alpha, int plain_unit, int down_splits, cudaStream_t stream) {
+    // down_splits: blm_moe_down_splits(...) of the same sizes; y holds that many planes [places][width]
     // plain_unit 0: the gated units, w_gu [experts][2 ff][width]; act_limit <= 0: silu(gate) * up; > 0: the clamped unit with
     // that limit and act_alpha.  plain_unit 1 (exact GELU) or 2 (tanh GELU): no gate, w_gu [experts][ff][width]
     if (n_tokens == 0) return BLM_OK;
@@ -540,6 +763,22 @@ BLM_API int blm_moe_experts(const void* h, int dtype, const float* weights, cons
     BLM_REQUIRE(tiles < (1ll << 31), "moe_experts: %lld tiles", tiles);
     const dim3 g1((unsigned)tiles, (unsigned)((ff + kBN - 1) / kBN)), g2((unsigned)tiles, (unsigned)((width + kBN - 1) / kBN));
     BLM_REQUIRE(g1.y <= 65535 && g2.y <= 65535, "moe_experts: too many output tiles");
+    BLM_REQUIRE(down_splits == blm_moe_down_splits(dtype, n_tokens, width, ff, n_experts, top), "moe_experts: %d planes of sums", down_splits);
+    if (moe_runs_skinny(dtype, pairs, width, ff, n_experts)) {
+        const long long t16 = (pairs + kSM - 1) / kSM + n_experts;
+        const dim3 s1((unsigned)t16, (unsigned)((ff + kSN - 1) / kSN)), s2((unsigned)t16, (unsigned)((width + kSN - 1) / kSN), (unsigned)down_splits);
+        BLM_REQUIRE(s1.y <= 65535 && s2.y <= 65535, "moe_experts: too many output tiles");
+        const int smem_up = 2 * (kSTileX + (plain_unit ? 1 : 2) * kSTileW) * (int)sizeof(__nv_bfloat16);
+        const int smem_down = 2 * (kSTileX + kSTileW) * (int)sizeof(__nv_bfloat16);
+        auto up_kernel = plain_unit ? moe_up_skinny_kernel<false> : moe_up_skinny_kernel<true>;
+        cudaError_t err = cudaFuncSetAttribute(up_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_up);
+        if (err != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "moe_experts: %s", cudaGetErrorString(err));
+        up_kernel<<<s1, 128, smem_up, stream>>>((const __nv_bfloat16*)h, weights, order, offsets, (const __nv_bfloat16*)w_gu,
+                                                (__nv_bfloat16*)act, width, ff, n_experts, top, scale_input, glu);
+        moe_down_skinny_kernel<<<s2, 128, smem_down, stream>>>((const __nv_bfloat16*)act, offsets, (const __nv_bfloat16*)w_down, y, width, ff,
+                                                               n_experts, pairs * width);
+        return blm_check_launch("moe_experts (few tokens an expert)");
+    }
     if (dtype == BLM_F32) {
         moe_gate_up_kernel<float><<<g1, 256, 0, stream>>>((const float*)h, weights, order, offsets, (const float*)w_gu, (float*)act, width,
                                                           ff, n_experts, top, scale_input, glu);
@@ -547,12 +786,15 @@ BLM_API int blm_moe_experts(const void* h, int dtype, const float* weights, cons
     } else if (dtype == BLM_BF16 && width % 8 == 0 && ff % 8 == 0) {
         const long long t64 = (pairs + kTM - 1) / kTM + n_experts;
         const dim3 t1((unsigned)t64, (unsigned)((ff + kTN - 1) / kTN)), t2((unsigned)t64, (unsigned)((width + kTN - 1) / kTN));
-        const int smem1 = 2 * 3 * kTile * (int)sizeof(__nv_bfloat16), smem2 = 2 * 2 * kTile * (int)sizeof(__nv_bfloat16);
+        const int smem1 = kMoeStages * (plain_unit ? 2 : 3) * kTile * (int)sizeof(__nv_bfloat16);
+        const int smem2 = kMoeStages * 2 * kTile * (int)sizeof(__nv_bfloat16);
         auto up_kernel = plain_unit ? moe_gate_up_tc_kernel<false> : moe_gate_up_tc_kernel<true>;
         cudaError_t err = cudaFuncSetAttribute(up_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1);
         if (err != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "moe_experts: %s", cudaGetErrorString(err));
         up_kernel<<<t1, 128, smem1, stream>>>((const __nv_bfloat16*)h, weights, order, offsets, (const __nv_bfloat16*)w_gu,
                                               (__nv_bfloat16*)act, width, ff, n_experts, top, scale_input, glu);
+        err = cudaFuncSetAttribute(moe_down_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2);
+        if (err != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "moe_experts: %s", cudaGetErrorString(err));
         moe_down_tc_kernel<<<t2, 128, smem2, stream>>>((const __nv_bfloat16*)act, offsets, (const __nv_bfloat16*)w_down, y, width, ff,
                                                        n_experts);
     } else if (dtype == BLM_BF16) {
@@ -568,16 +810,20 @@ BLM_API int blm_moe_experts(const void* h, int dtype, const float* weights, cons
 }
 
 // ---------------------------------------------------------------------------------------------
-// out[n] = sum_k (weight_k if the weight is on the output) y[place_of[n, k]] + extra[n]   (k in the order of the choice)
+// out[n] = sum_k (weight_k if the weight is on the output) y[place_of[n, k]] + extra[n]   (k in the order of the choice);
+// y may come in n_planes planes of [places][width] whose sum it is
 // ---------------------------------------------------------------------------------------------
 template <typename T, typename TO>
 __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place_of, const float* __restrict__ weights,
-                                   const T* __restrict__ extra, TO* __restrict__ out, int width, int top, int scale_output) {
+                                   const T* __restrict__ extra, TO* __restrict__ out, int width, int top, int scale_output, int n_planes,
+                                   long long plane) {
     const int n = blockIdx.x;
     for (int d = threadIdx.x; d < width; d += blockDim.x) {
         float s = 0.f;
         for (int k = 0; k < top; ++k) {
-            const float v = y[(size_t)place_of[(size_t)n * top + k] * width + d];
+            const size_t at = (size_t)place_of[(size_t)n * top + k] * width + d;
+            float v = y[at];
+            for (int z = 1; z < n_planes; ++z) v += y[at + (size_t)z * plane];      // the shares of a cut reduction, in order
             s += scale_output ? weights[(size_t)n * top + k] * v : v;
         }
         if (extra) s += to_f32(extra[(size_t)n * width + d]);
@@ -586,20 +832,21 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
 }
 
 BLM_API int blm_moe_combine(const float* y, const int* place_of, const float* weights, const void* extra, void* out, int dtype,
-                            int n_tokens, int width, int top, int scale_output, int out_dtype, cudaStream_t stream) {
+                            int n_tokens, int width, int top, int scale_output, int out_dtype, int n_planes, cudaStream_t stream) {
     // dtype: that of `extra`; out_dtype: that of `out` (the same, or float32: the sum handed on unrounded)
     if (n_tokens == 0) return BLM_OK;
-    BLM_REQUIRE(n_tokens > 0 && width > 0 && top > 0, "moe_combine: bad sizes");
+    BLM_REQUIRE(n_tokens > 0 && width > 0 && top > 0 && n_planes >= 1, "moe_combine: bad sizes");
+    const long long plane = (long long)n_tokens * top * width;
     if (dtype == BLM_BF16 && out_dtype == BLM_F32)
         moe_combine_kernel<__nv_bfloat16, float><<<n_tokens, 256, 0, stream>>>(y, place_of, weights, (const __nv_bfloat16*)extra,
-                                                                               (float*)out, width, top, scale_output);
+                                                                               (float*)out, width, top, scale_output, n_planes, plane);
     else if (dtype != out_dtype)
         return blm_fail(BLM_BAD_ARGUMENT, "moe_combine: dtype %d with out dtype %d", dtype, out_dtype);
     else if (dtype == BLM_F32)
-        moe_combine_kernel<float, float><<<n_tokens, 256, 0, stream>>>(y, place_of, weights, (const float*)extra, (float*)out, width, top, scale_output);
+        moe_combine_kernel<float, float><<<n_tokens, 256, 0, stream>>>(y, place_of, weights, (const float*)extra, (float*)out, width, top, scale_output, n_planes, plane);
     else if (dtype == BLM_BF16)
         moe_combine_kernel<__nv_bfloat16, __nv_bfloat16><<<n_tokens, 256, 0, stream>>>(y, place_of, weights, (const __nv_bfloat16*)extra,
-                                                                                       (__nv_bfloat16*)out, width, top, scale_output);
+                                                                                       (__nv_bfloat16*)out, width, top, scale_output, n_planes, plane);
     else
         return blm_fail(BLM_BAD_ARGUMENT, "moe_combine: dtype %d", dtype);
     return blm_check_launch("moe_combine");

@@ -155,8 +155,9 @@ _protos = {
                           c_void_p],
         "blm_moe_group": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
         "blm_moe_experts": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                            c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p],
-        "blm_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                            c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_void_p],
+        "blm_moe_down_splits": [c_int, c_int, c_int, c_int, c_int, c_int],
+        "blm_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     },
     "attention": {
         "blm_attention": [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
@@ -521,14 +522,16 @@ def moe_experts(h, ids, weights, gate_up, down, extra=None, weight_on_input=True
     order = torch.empty(pairs, dtype=torch.int32, device=dev)
     place_of = torch.empty(pairs, dtype=torch.int32, device=dev)
     act = torch.empty((pairs, ff), dtype=h.dtype, device=dev)
-    y = torch.empty((pairs, d), dtype=torch.float32, device=dev)
+    # steps that bring an expert a few tokens cut the second product's reduction over several blocks: a plane of sums each
+    planes = int(_lib("moe").blm_moe_down_splits(_code(h.dtype), n, d, ff, e, top))
+    y = torch.empty((planes, pairs, d), dtype=torch.float32, device=dev)
     out = torch.empty((n, d), dtype=out_dtype or h.dtype, device=dev)
     stream = _stream()
     _call("moe", "blm_moe_group", _ptr(ids), pairs, e, _ptr(offsets), _ptr(order), _ptr(place_of), stream)
     _call("moe", "blm_moe_experts", _ptr(h), _code(h.dtype), _ptr(weights), _ptr(order), _ptr(offsets), _ptr(gate_up), _ptr(down),
-          _ptr(act), _ptr(y), n, d, ff, e, top, 1 if weight_on_input else 0, c_float(clamp_limit), c_float(clamp_alpha), int(unit), stream, kernels=2)
+          _ptr(act), _ptr(y), n, d, ff, e, top, 1 if weight_on_input else 0, c_float(clamp_limit), c_float(clamp_alpha), int(unit), planes, stream, kernels=2)
     _call("moe", "blm_moe_combine", _ptr(y), _ptr(place_of), _ptr(weights), _ptr(extra), _ptr(out), _code(h.dtype), n, d, top,
-          0 if weight_on_input else 1, _code(out.dtype), stream)
+          0 if weight_on_input else 1, _code(out.dtype), planes, stream)
     return out
 
 

@@ -83,6 +83,10 @@ class LatentAttention(Part):
         self.down_cols = spec.rank + spec.rot_dim
         self.v_cols = spec.n_heads * spec.value_dim
         self.gate_cols = spec.n_heads if spec.gate_per_head else self.v_cols
+        # long portions run the grouped-query kernels on keys and values written out: the windowed family's with a window
+        # or a sink, the dense decoder's without (only the one this mixer uses is compiled before the first step)
+        self.kernel_modules = ("elementwise", "attention_latent", "gemm",
+                               "attention_sink" if spec.window is not None or spec.sink else "attention")
 
     def tensor_specs(self):
         s, t = self.spec, self.tensor_names

@@ -70,7 +70,7 @@ def test_what_the_runs_keep():
     assert (needs[1].head_dim, needs[1].window) == (32 + 16, 20) and (needs[3].head_dim, needs[3].window) == (48 + 8, 70)
     # the block reads the stream itself: what stands where its first norm would takes a pending normed output
     assert model.layers[0].block.first_norm().takes_post_normed
-    assert sorted(model.kernel_modules()) == ["attention", "attention_latent", "attention_sink", "elementwise", "gemm", "moe", "stream_ops"]
+    assert sorted(model.kernel_modules()) == ["attention_latent", "attention_sink", "elementwise", "gemm", "moe", "stream_ops"]
 
 
 def test_folders_hold_what_the_plain_implementation_reads(tmp_path):
