@@ -42,7 +42,7 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
             const float4* w4 = reinterpret_cast<const float4*>(w);
             const float4* x4 = reinterpret_cast<const float4*>(x);
             float z0 = 0.f, z1 = 0.f, z2 = 0.f, z3 = 0.f;
-#pragma unroll 4
+#pragma unroll 8
             for (int d = lane; d < width / 4; d += 32) {
                 const float4 a = __ldg(w4 + d), c = x4[d];
                 z0 = fmaf(a.x, c.x, z0); z1 = fmaf(a.y, c.y, z1); z2 = fmaf(a.z, c.z, z2); z3 = fmaf(a.w, c.w, z3);
@@ -133,11 +133,13 @@ BLM_API int blm_moe_route(const void* h, int dtype, const float* router, int n_t
                 "moe_route: %d experts in %d groups of which %d are kept, for %d chosen", n_experts, n_groups, keep_groups, top);
     const size_t smem = ((size_t)width + 2 * n_experts + n_groups) * sizeof(float);
     BLM_REQUIRE(smem <= 48 * 1024, "moe_route: width %d and %d experts need %zu bytes of shared memory", width, n_experts, smem);
+    // a warp an expert where the experts are few (the warps' dot products wait for memory side by side), sixteen warps at most
+    const int threads = n_experts <= 4 ? 128 : (n_experts >= 16 ? 512 : 32 * n_experts);
     if (dtype == BLM_F32)
-        moe_route_kernel<float><<<n_tokens, 128, smem, stream>>>((const float*)h, router, width, n_experts, top, ids, weights, softmax,
+        moe_route_kernel<float><<<n_tokens, threads, smem, stream>>>((const float*)h, router, width, n_experts, top, ids, weights, softmax,
                                                                  correction, renorm, n_groups, keep_groups);
     else if (dtype == BLM_BF16)
-        moe_route_kernel<__nv_bfloat16><<<n_tokens, 128, smem, stream>>>((const __nv_bfloat16*)h, router, width, n_experts, top, ids,
+        moe_route_kernel<__nv_bfloat16><<<n_tokens, threads, smem, stream>>>((const __nv_bfloat16*)h, router, width, n_experts, top, ids,
                                                                          weights, softmax, correction, renorm, n_groups, keep_groups);
     else
         return blm_fail(BLM_BAD_ARGUMENT, "moe_route: dtype %d", dtype);
