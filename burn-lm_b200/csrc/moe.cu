@@ -732,6 +732,200 @@ __global__ void __launch_bounds__(128) moe_down_skinny_kernel(const __nv_bfloat1
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// And for prompts that bring an expert a hundred tokens and more: tiles of 128 places x 128 outputs (with a gate: 64
+// outputs, their gate rows and their up rows side by side as the tile's 128 weight rows), eight warps in two rows of four,
+// a warp 64 places x 32 weight rows in registers, the reduction in slices of 64 lanes through three buffers.  A warp
+// issues 16 mma for 6 ldmatrix where the 64-place kernels issue 8 for 5, and a weight row fetched from L2 serves twice
+// the places.
+// ---------------------------------------------------------------------------------------------
+constexpr int kWM = 128, kWN = 128, kWK = 64, kWStride = kWK + 8, kWStages = 3;
+constexpr int kWTile = kWM * kWStride;
+#ifndef BLM_MOE_WIDE_PAIRS
+#define BLM_MOE_WIDE_PAIRS 96        // from this many (token, expert) pairs an expert on average the wide kernels run
+#endif
+
+// one slice: acc[mi][ni] += x (64 places of the warp) . w (the warp's 32 weight rows: two runs of 16 at rb0 and rb1)
+__device__ __forceinline__ void moe_wide_slice(float (&acc)[4][4][4], unsigned xs, unsigned ws, int wm, int rb0, int rb1, int lrow, int lmat) {
+#pragma unroll
+    for (int kk = 0; kk < kWK; kk += 16) {
+        uint32_t a[4][4], b0[4], b1[4];
+#pragma unroll
+        for (int mi = 0; mi < 4; ++mi)
+            moe_ldsm_x4(a[mi], xs + ((wm * 64 + mi * 16 + lrow + (lmat & 1) * 8) * kWStride + kk + (lmat >> 1) * 8) * 2);
+        moe_ldsm_x4(b0, ws + ((rb0 + lrow + (lmat >> 1) * 8) * kWStride + kk + (lmat & 1) * 8) * 2);
+        moe_ldsm_x4(b1, ws + ((rb1 + lrow + (lmat >> 1) * 8) * kWStride + kk + (lmat & 1) * 8) * 2);
+#pragma unroll
+        for (int mi = 0; mi < 4; ++mi) {
+            moe_mma(acc[mi][0], a[mi], b0[0], b0[1]);
+            moe_mma(acc[mi][1], a[mi], b0[2], b0[3]);
+            moe_mma(acc[mi][2], a[mi], b1[0], b1[1]);
+            moe_mma(acc[mi][3], a[mi], b1[2], b1[3]);
+        }
+    }
+}
+
+template <bool kGated>
+__global__ void __launch_bounds__(256) moe_up_wide_kernel(const __nv_bfloat16* __restrict__ h, const float* __restrict__ weights,
+                                                          const int* __restrict__ order, const int* __restrict__ offsets,
+                                                          const __nv_bfloat16* __restrict__ w_gu, __nv_bfloat16* __restrict__ act,
+                                                          int width, int ff, int n_experts, int top, int scale_input, GluAct glu) {
+    extern __shared__ __align__(16) unsigned char moe_smem[];
+    __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(moe_smem);      // kWStages x (x [128], weight rows [128])
+    __shared__ int token_of[kWM];
+    __shared__ float scale_of[kWM];
+    int e, first, last;
+    if (!moe_find_tile(offsets, n_experts, blockIdx.x, &e, &first, &last, kWM)) return;
+    constexpr int kOut = kGated ? kWN / 2 : kWN;           // outputs of a tile
+    const int c0 = blockIdx.y * kOut;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, quad = lane >> 2, pair = (lane & 3) * 2;
+    const int lrow = lane & 7, lmat = lane >> 3, wm = warp >> 2, wn = warp & 3;
+    if (threadIdx.x < kWM) {
+        const int place = first + threadIdx.x;
+        int tok = -1;
+        float sc = 1.f;
+        if (place < last) {
+            const int p = order[place];
+            tok = p / top;
+            if (scale_input) sc = weights[p];
+        }
+        token_of[threadIdx.x] = tok;
+        scale_of[threadIdx.x] = sc;
+    }
+    __syncthreads();
+    const __nv_bfloat16* wg = w_gu + (size_t)e * (kGated ? 2 : 1) * ff * width;
+    auto stage_slice = [&](int buf, int k0) {
+        __nv_bfloat16* xs = stage + buf * 2 * kWTile;
+        for (int idx = threadIdx.x; idx < kWM * (kWK / 8); idx += blockDim.x) {
+            const int r = idx / (kWK / 8), kk = (idx % (kWK / 8)) * 8;
+            const int tok = token_of[r];
+            const bool in = tok >= 0 && k0 + kk < width;
+            moe_cp16(xs + r * kWStride + kk, in ? h + (size_t)tok * width + k0 + kk : h, in);
+        }
+        for (int idx = threadIdx.x; idx < kWN * (kWK / 8); idx += blockDim.x) {
+            const int r = idx / (kWK / 8), kk = (idx % (kWK / 8)) * 8;
+            // with a gate: rows 0 .. 63 the gate rows of the tile's outputs, rows 64 .. 127 their up rows (ff rows further on)
+            const int c = kGated ? c0 + (r & (kOut - 1)) : c0 + r;
+            const bool in = c < ff && k0 + kk < width;
+            const size_t row = kGated && r >= kOut ? (size_t)ff + c : (size_t)c;
+            moe_cp16(xs + kWTile + r * kWStride + kk, in ? wg + row * width + k0 + kk : wg, in);
+        }
+    };
+    float acc[4][4][4];
+#pragma unroll
+    for (int mi = 0; mi < 4; ++mi)
+#pragma unroll
+        for (int ni = 0; ni < 4; ++ni) acc[mi][ni][0] = acc[mi][ni][1] = acc[mi][ni][2] = acc[mi][ni][3] = 0.f;
+    const int rb0 = kGated ? wn * 16 : wn * 32, rb1 = kGated ? kOut + wn * 16 : wn * 32 + 16;
+    const unsigned stage_at = (unsigned)__cvta_generic_to_shared(stage);
+    const int n_slices = (width + kWK - 1) / kWK;
+#pragma unroll
+    for (int ahead = 0; ahead < kWStages - 1; ++ahead) {
+        if (ahead < n_slices) stage_slice(ahead, ahead * kWK);
+        moe_cp_commit();
+    }
+    for (int it = 0; it < n_slices; ++it) {
+        const int buf = it % kWStages;
+        if (it + kWStages - 1 < n_slices) stage_slice((it + kWStages - 1) % kWStages, (it + kWStages - 1) * kWK);
+        moe_cp_commit();
+        moe_cp_wait_all_but<kWStages - 1>();
+        __syncthreads();
+        const unsigned xs = stage_at + buf * 2 * kWTile * 2;
+        moe_wide_slice(acc, xs, xs + kWTile * 2, wm, rb0, rb1, lrow, lmat);
+        __syncthreads();
+    }
+#pragma unroll
+    for (int mi = 0; mi < 4; ++mi)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r = wm * 64 + mi * 16 + quad + 8 * half, place = first + r;
+            if (place >= last) continue;
+            const float sc = scale_of[r];
+            if (kGated) {
+#pragma unroll
+                for (int ni = 0; ni < 2; ++ni) {
+                    const int c = c0 + wn * 16 + 8 * ni + pair;
+                    if (c < ff)
+                        *reinterpret_cast<__nv_bfloat162*>(act + (size_t)place * ff + c) = __floats2bfloat162_rn(
+                            glu_act(sc * acc[mi][ni][2 * half], sc * acc[mi][ni + 2][2 * half], glu),
+                            glu_act(sc * acc[mi][ni][2 * half + 1], sc * acc[mi][ni + 2][2 * half + 1], glu));
+                }
+            } else {
+#pragma unroll
+                for (int ni = 0; ni < 4; ++ni) {
+                    const int c = c0 + wn * 32 + 8 * ni + pair;
+                    if (c < ff)
+                        *reinterpret_cast<__nv_bfloat162*>(act + (size_t)place * ff + c) = __floats2bfloat162_rn(
+                            glu_act(sc * acc[mi][ni][2 * half], 0.f, glu), glu_act(sc * acc[mi][ni][2 * half + 1], 0.f, glu));
+                }
+            }
+        }
+}
+
+__global__ void __launch_bounds__(256) moe_down_wide_kernel(const __nv_bfloat16* __restrict__ act, const int* __restrict__ offsets,
+                                                            const __nv_bfloat16* __restrict__ w_down, float* __restrict__ y, int width, int ff,
+                                                            int n_experts) {
+    extern __shared__ __align__(16) unsigned char moe_smem[];
+    __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(moe_smem);      // kWStages x (x [128], weight rows [128])
+    int e, first, last;
+    if (!moe_find_tile(offsets, n_experts, blockIdx.x, &e, &first, &last, kWM)) return;
+    const int c0 = blockIdx.y * kWN;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, quad = lane >> 2, pair = (lane & 3) * 2;
+    const int lrow = lane & 7, lmat = lane >> 3, wm = warp >> 2, wn = warp & 3;
+    const __nv_bfloat16* wd = w_down + (size_t)e * width * ff;
+    auto stage_slice = [&](int buf, int k0) {
+        __nv_bfloat16* xs = stage + buf * 2 * kWTile;
+        for (int idx = threadIdx.x; idx < kWM * (kWK / 8); idx += blockDim.x) {
+            const int r = idx / (kWK / 8), kk = (idx % (kWK / 8)) * 8;
+            const bool in = first + r < last && k0 + kk < ff;
+            moe_cp16(xs + r * kWStride + kk, in ? act + (size_t)(first + r) * ff + k0 + kk : act, in);
+        }
+        for (int idx = threadIdx.x; idx < kWN * (kWK / 8); idx += blockDim.x) {
+            const int r = idx / (kWK / 8), kk = (idx % (kWK / 8)) * 8;
+            const bool in = c0 + r < width && k0 + kk < ff;
+            moe_cp16(xs + kWTile + r * kWStride + kk, in ? wd + (size_t)(c0 + r) * ff + k0 + kk : wd, in);
+        }
+    };
+    float acc[4][4][4];
+#pragma unroll
+    for (int mi = 0; mi < 4; ++mi)
+#pragma unroll
+        for (int ni = 0; ni < 4; ++ni) acc[mi][ni][0] = acc[mi][ni][1] = acc[mi][ni][2] = acc[mi][ni][3] = 0.f;
+    const unsigned stage_at = (unsigned)__cvta_generic_to_shared(stage);
+    const int n_slices = (ff + kWK - 1) / kWK;
+#pragma unroll
+    for (int ahead = 0; ahead < kWStages - 1; ++ahead) {
+        if (ahead < n_slices) stage_slice(ahead, ahead * kWK);
+        moe_cp_commit();
+    }
+    for (int it = 0; it < n_slices; ++it) {
+        const int buf = it % kWStages;
+        if (it + kWStages - 1 < n_slices) stage_slice((it + kWStages - 1) % kWStages, (it + kWStages - 1) * kWK);
+        moe_cp_commit();
+        moe_cp_wait_all_but<kWStages - 1>();
+        __syncthreads();
+        const unsigned xs = stage_at + buf * 2 * kWTile * 2;
+        moe_wide_slice(acc, xs, xs + kWTile * 2, wm, wn * 32, wn * 32 + 16, lrow, lmat);
+        __syncthreads();
+    }
+#pragma unroll
+    for (int mi = 0; mi < 4; ++mi)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int place = first + wm * 64 + mi * 16 + quad + 8 * half;
+            if (place >= last) continue;
+#pragma unroll
+            for (int ni = 0; ni < 4; ++ni) {
+                const int c = c0 + wn * 32 + 8 * ni + pair;
+                if (c < width) *reinterpret_cast<float2*>(y + (size_t)place * width + c) = make_float2(acc[mi][ni][2 * half], acc[mi][ni][2 * half + 1]);
+            }
+        }
+}
+
+static bool moe_runs_wide(int dtype, long long pairs, int width, int ff, int n_experts) {
+    return dtype == BLM_BF16 && width % 8 == 0 && ff % 8 == 0 && pairs >= (long long)BLM_MOE_WIDE_PAIRS * n_experts;
+}
+
 static bool moe_runs_skinny(int dtype, long long pairs, int width, int ff, int n_experts) {
     return dtype == BLM_BF16 && width % 8 == 0 && ff % 8 == 0 && pairs <= (long long)BLM_MOE_SKINNY_PAIRS * n_experts;
 }
@@ -780,6 +974,22 @@ BLM_API int blm_moe_experts(const void* h, int dtype, const float* weights, cons
         moe_down_skinny_kernel<<<s2, 128, smem_down, stream>>>((const __nv_bfloat16*)act, offsets, (const __nv_bfloat16*)w_down, y, width, ff,
                                                                n_experts, pairs * width);
         return blm_check_launch("moe_experts (few tokens an expert)");
+    }
+    if (moe_runs_wide(dtype, pairs, width, ff, n_experts)) {
+        const long long t128 = (pairs + kWM - 1) / kWM + n_experts;
+        const int outs = plain_unit ? kWN : kWN / 2;
+        const dim3 w1((unsigned)t128, (unsigned)((ff + outs - 1) / outs)), w2((unsigned)t128, (unsigned)((width + kWN - 1) / kWN));
+        BLM_REQUIRE(w1.y <= 65535 && w2.y <= 65535, "moe_experts: too many output tiles");
+        const int smem = kWStages * 2 * kWTile * (int)sizeof(__nv_bfloat16);
+        auto up_kernel = plain_unit ? moe_up_wide_kernel<false> : moe_up_wide_kernel<true>;
+        cudaError_t err = cudaFuncSetAttribute(up_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (err == cudaSuccess) err = cudaFuncSetAttribute(moe_down_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (err != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "moe_experts: %s", cudaGetErrorString(err));
+        up_kernel<<<w1, 256, smem, stream>>>((const __nv_bfloat16*)h, weights, order, offsets, (const __nv_bfloat16*)w_gu,
+                                             (__nv_bfloat16*)act, width, ff, n_experts, top, scale_input, glu);
+        moe_down_wide_kernel<<<w2, 256, smem, stream>>>((const __nv_bfloat16*)act, offsets, (const __nv_bfloat16*)w_down, y, width, ff,
+                                                        n_experts);
+        return blm_check_launch("moe_experts (many tokens an expert)");
     }
     if (dtype == BLM_F32) {
         moe_gate_up_kernel<float><<<g1, 256, 0, stream>>>((const float*)h, weights, order, offsets, (const float*)w_gu, (float*)act, width,

@@ -273,7 +273,7 @@ def planted_latent(n, j, window, dr=16, R=32, dv=24):
 
 @pytest.mark.parametrize("dtype,tol", [("float32", 2e-4), ("bfloat16", 3e-2)])
 @pytest.mark.parametrize("decoded", [False, True])
-@pytest.mark.parametrize("n,window,back", [(300, 72, 71), (300, 72, 72), (300, 64, 63), (300, 64, 64), (300, 65, 64), (300, 65, 65),
+@pytest.mark.parametrize("n,window,back", [(300, 75, 74), (300, 75, 75), (300, 64, 63), (300, 64, 64), (300, 65, 64), (300, 65, 65),
                                            (300, 1, 0), (300, 2, 1), (300, 2, 2), (70, 200, 69), (130, 129, 128), (130, 128, 128)])
 def test_a_key_just_inside_and_just_outside_the_window(n, window, back, decoded, dtype, tol):
     j = n - 1 - back
@@ -327,7 +327,7 @@ def test_the_norm_behind_a_sublayer_joins_the_stream_which_is_handed_on_as_it_is
 
 
 # the experts ---------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("n_experts,top,groups,keep", [(12, 2, 4, 3), (8, 2, 4, 2), (6, 3, 2, 1), (5, 2, 5, 3), (4, 4, 1, 1), (16, 4, 8, 2), (1, 1, 1, 1), (6, 2, 3, 3)])
+@pytest.mark.parametrize("n_experts,top,groups,keep", [(12, 3, 3, 2), (8, 2, 4, 2), (6, 3, 2, 1), (5, 2, 5, 3), (4, 4, 1, 1), (16, 4, 8, 2), (1, 1, 1, 1), (6, 2, 3, 3)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_routing_by_groups_and_experts_without_a_gate(n_experts, top, groups, keep, dtype):
     from burn_lm_b200 import kernels as K
@@ -369,6 +369,35 @@ def test_experts_of_odd_sizes_and_of_large_ones():
         got = K.moe_experts(dev(hp, dtype), ids, weights, up, down, weight_on_input=False, out_dtype=torch.float32, unit=K.UNIT_GELU)
         want = P.experts(hp, w, f, "m.")
         assert np.abs(got.cpu().numpy() - want).max() < (2e-5 if dtype == torch.float32 else 3e-2) * np.abs(want).max()
+
+
+@pytest.mark.parametrize("n,width,ff,n_experts,top", [(700, 136, 72, 4, 2), (1100, 64, 264, 3, 1), (520, 128, 128, 2, 2)])
+def test_experts_with_many_tokens_an_expert(n, width, ff, n_experts, top):
+    """Prompts run other kernels than single tokens do (larger tiles); with and without a gate, against the plain
+    implementation and against the 32-bit kernels."""
+    from burn_lm_b200 import kernels as K
+    rng = np.random.default_rng(n)
+    f = experts(n_experts, top, ff, 1, 1)
+    hp = bf(rng.normal(size=(n, width)))
+    w = {"m.router": bf(2.0 * rng.normal(size=(n_experts, width)) / np.sqrt(width)), "m.correction": np.zeros(n_experts)}
+    for e in range(n_experts):
+        w[f"m.e{e}.up"], w[f"m.e{e}.down"] = bf(2.0 * rng.normal(size=(ff, width)) / np.sqrt(width)), bf(rng.normal(size=(width, ff)) / np.sqrt(ff))
+    gate = bf(2.0 * rng.normal(size=(n_experts, ff, width)) / np.sqrt(width))
+    want = P.experts(hp, w, f, "m.")
+    outs = {}
+    for dtype in (torch.float32, torch.bfloat16):
+        ids, weights = K.moe_route(dev(hp, dtype), dev(w["m.router"]), top)
+        up = dev(np.stack([w[f"m.e{e}.up"] for e in range(n_experts)]), dtype)
+        down = dev(np.stack([w[f"m.e{e}.down"] for e in range(n_experts)]), dtype)
+        got = K.moe_experts(dev(hp, dtype), ids, weights, up, down, weight_on_input=False, out_dtype=torch.float32, unit=K.UNIT_GELU)
+        assert np.abs(got.cpu().numpy() - want).max() < (2e-5 if dtype == torch.float32 else 3e-2) * np.abs(want).max()
+        gate_up = torch.cat([dev(gate, dtype), up], dim=1).contiguous()
+        for on_input in (False, True):
+            outs[dtype, on_input] = K.moe_experts(dev(hp, dtype), ids, weights, gate_up, down, weight_on_input=on_input,
+                                                  out_dtype=torch.float32).cpu().numpy()
+    for on_input in (False, True):
+        exact = outs[torch.float32, on_input]
+        assert np.abs(outs[torch.bfloat16, on_input] - exact).max() < 3e-2 * np.abs(exact).max()
 
 
 def test_a_gate_per_head():
