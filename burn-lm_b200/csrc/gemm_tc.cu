@@ -16,6 +16,13 @@
 // (one writer per element), so a prompt step's output and down products need no bf16 round trip.  Edges: the TMA fills what lies outside x or W with zeros, the epilogue
 // stores only what lies inside y.
 //
+// Grouped form (blm_gemm_tc_grouped): the rows of x are the (token, expert) pairs of a mixture of experts, laid out expert by
+// expert with every expert's share starting at a multiple of 128 rows, and W is the experts' weights one below the other
+// ([experts x N, K]).  A table on the device names the expert of every tile of 128 rows (-1: a tile no expert owns); a block
+// looks its tile's expert up and fetches W's tiles from that expert's rows.  The tensor maps cover the whole buffers, so they
+// depend on sizes and addresses only and a step can be captured.  Its epilogues: the exact GELU (an expert without a gate),
+// and fp32 sums stored as they are.
+//
 // Every mbarrier wait is bounded; a wait that runs out records a code in the caller's status word and
 // the block goes on to its end, where the tensor memory is given back.
 #include <cuda.h>
@@ -36,7 +43,7 @@ constexpr int kTmemCols = 512;                  // two fp32 accumulators of 256 
 constexpr unsigned kABytes = BM * BK * 2, kBBytes = BN * BK * 2;
 constexpr unsigned kSpinLimit = 1u << 22;
 
-enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_RESID_ADD = 2 };
+enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_RESID_ADD = 2, EPI_GELU = 3, EPI_STORE_F32 = 4 };
 enum { TC_OK = 0, TC_TIMEOUT_FULL = 11, TC_TIMEOUT_EMPTY = 12, TC_TIMEOUT_ACCUM = 13, TC_TIMEOUT_DRAIN = 14 };
 
 struct TcArgs {
@@ -46,6 +53,8 @@ struct TcArgs {
     int M, N, K;        // N: rows of W
     int epi;
     int* status;
+    const int* tile_expert;     // grouped form: the expert of every tile of BM rows (-1: none); null: one weight for all rows
+    int expert_rows;            // grouped form: rows of W an expert (the next expert's rows follow)
 };
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -149,6 +158,18 @@ __device__ __forceinline__ void store_columns(const TcArgs& a, const float (&v)[
         }
         return;
     }
+    if (EPI == EPI_STORE_F32) {
+        const int c0 = n0 + j * 16;
+        if (c0 >= a.N) return;
+        float* dst = a.acc + (size_t)row * a.ldy + c0;
+        if (c0 + 16 <= a.N && ((a.ldy & 3) == 0)) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) reinterpret_cast<float4*>(dst)[e] = make_float4(v[4 * e], v[4 * e + 1], v[4 * e + 2], v[4 * e + 3]);
+        } else {
+            for (int e = 0; e < 16 && c0 + e < a.N; ++e) dst[e] = v[e];
+        }
+        return;
+    }
     if (EPI == EPI_SWIGLU) {
         const int inner = a.N >> 1, o0 = (n0 >> 1) + j * 8;
         if (o0 >= inner) return;
@@ -172,7 +193,12 @@ __device__ __forceinline__ void store_columns(const TcArgs& a, const float (&v)[
         unsigned packed[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-            const __nv_bfloat162 p = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+            float lo = v[2 * e], hi = v[2 * e + 1];
+            if (EPI == EPI_GELU) {           // the exact form: z (1 + erf(z / sqrt 2)) / 2
+                lo = 0.5f * lo * (1.0f + erff(lo * 0.70710678118654752f));
+                hi = 0.5f * hi * (1.0f + erff(hi * 0.70710678118654752f));
+            }
+            const __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
             packed[e] = *reinterpret_cast<const unsigned*>(&p);
         }
         __nv_bfloat16* dst = a.y + (size_t)row * a.ldy + c0;
@@ -233,6 +259,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs a, co
             bool ok = true;
             for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
                 const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+                int w0 = n0;                 // W's first row of the tile
+                if (a.tile_expert != nullptr) {
+                    const int e = a.tile_expert[tile % m_tiles];
+                    if (e < 0) continue;     // a tile of rows no expert owns: every role of the block passes it by
+                    w0 += e * a.expert_rows;
+                }
                 for (int k = 0; k < k_iters; ++k, ++it) {
                     const int s = it % kStages;
                     if (it >= (unsigned)kStages && !mbar_wait(empty + s, ((it / kStages) - 1) & 1)) {
@@ -242,7 +274,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs a, co
                     }
                     mbar_expect_tx(full + s, kABytes + kBBytes);
                     tma_load_2d(As + s * kABytes, &xmap, k * BK, m0, full + s);
-                    tma_load_2d(Bs + s * kBBytes, &wmap, k * BK, n0, full + s);
+                    tma_load_2d(Bs + s * kBBytes, &wmap, k * BK, w0, full + s);
                 }
             }
         }
@@ -254,7 +286,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs a, co
             bool ok = true;
             // operand descriptors: the address field counts 16 bytes, so a stage further is an addition
             const unsigned long long a_desc = umma_desc(As), b_desc = umma_desc(Bs);
-            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++n_tile) {
+            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+                if (a.tile_expert != nullptr && a.tile_expert[tile % m_tiles] < 0) continue;
                 const int b = n_tile & 1;
                 if (n_tile >= 2 && !mbar_wait(acc_empty + b, ((n_tile >> 1) - 1) & 1)) {      // the epilogue has read this accumulator
                     atomicCAS(a.status, TC_OK, TC_TIMEOUT_DRAIN);
@@ -278,13 +311,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs a, co
                     umma_commit(empty + s);                   // the stage is free when these products have read it
                 }
                 umma_commit(acc_full + b);                    // the accumulator is complete when everything issued is done
+                ++n_tile;
             }
         }
     } else {
         // ---------------- epilogue: warp w reads lanes 32 (w % 4) .. of the accumulators ----------------
         const int quarter = warp & 3;
         int n_tile = 0;
-        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++n_tile) {
+        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+            if (a.tile_expert != nullptr && a.tile_expert[tile % m_tiles] < 0) continue;
             const int b = n_tile & 1;
             const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
             if (!mbar_wait(acc_full + b, (n_tile >> 1) & 1)) {
@@ -303,6 +338,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(const TcArgs a, co
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty + b);        // this warp has read its quarter
+            ++n_tile;
         }
     }
     // everybody meets; then the warp that took the tensor memory gives it back
@@ -377,6 +413,7 @@ BLM_API int blm_gemm_tc(const void* x, long long ldx, const void* w, long long l
     if (rc != BLM_OK) return rc;
     TcArgs a;
     a.y = (__nv_bfloat16*)y; a.acc = (float*)y; a.ldy = ldy; a.M = M; a.N = N; a.K = K; a.epi = epi; a.status = status;
+    a.tile_expert = nullptr; a.expert_rows = 0;
     const size_t smem = (size_t)kStages * (kABytes + kBBytes) + (2 * kStages + 4) * 8 + 16 + 1024;
     static bool opted_in = false;
     if (!opted_in) {
@@ -392,4 +429,41 @@ BLM_API int blm_gemm_tc(const void* x, long long ldx, const void* w, long long l
     else if (epi == EPI_RESID_ADD) gemm_tc_kernel<EPI_RESID_ADD><<<grid, kThreads, smem, stream>>>(a, xmap, wmap);
     else gemm_tc_kernel<EPI_STORE><<<grid, kThreads, smem, stream>>>(a, xmap, wmap);
     return blm_check_launch("gemm_tc");
+}
+
+
+// The grouped form.  x bfloat16 [M, K] (row stride ldx): the pairs' rows expert by expert, every expert's share starting at a
+// multiple of 128 rows, M a multiple of 128 (rows no pair owns hold zeros); w bfloat16 [n_experts x N, K] (row stride ldw);
+// tile_expert int32 [M / 128] on the device: the expert of every tile of rows, -1 for a tile no expert owns.
+// epi 3: y bfloat16 [M, N] = gelu(x . w_e^T), the exact form; epi 4: y float32 [M, N] = x . w_e^T.
+BLM_API int blm_gemm_tc_grouped(const void* x, long long ldx, const void* w, long long ldw, void* y, long long ldy, int M, int N, int K,
+                                int n_experts, const int* tile_expert, int epi, int* status, cudaStream_t stream) {
+    if (M == 0 || N == 0) return BLM_OK;
+    BLM_REQUIRE(blm_gemm_tc_supported(M, N, K) && M % BM == 0 && n_experts >= 1, "gemm_tc_grouped: shape %d x %d x %d, %d experts", M, N, K, n_experts);
+    BLM_REQUIRE(ldx % 8 == 0 && ldw % 8 == 0 && ((size_t)x & 15) == 0 && ((size_t)w & 15) == 0,
+                "gemm_tc_grouped: operand rows must be 16-byte aligned");
+    BLM_REQUIRE(epi == EPI_GELU || epi == EPI_STORE_F32, "gemm_tc_grouped: epilogue %d", epi);
+    BLM_REQUIRE(status != nullptr && tile_expert != nullptr, "gemm_tc_grouped: no status word or no table of tiles");
+    BLM_REQUIRE((long long)n_experts * N < (1ll << 31), "gemm_tc_grouped: %d experts of %d rows", n_experts, N);
+    CUtensorMap xmap, wmap;
+    int rc = make_map(x, ldx, M, K, BM, false, &xmap);
+    if (rc != BLM_OK) return rc;
+    rc = make_map(w, ldw, n_experts * N, K, BN, true, &wmap);
+    if (rc != BLM_OK) return rc;
+    TcArgs a;
+    a.y = (__nv_bfloat16*)y; a.acc = (float*)y; a.ldy = ldy; a.M = M; a.N = N; a.K = K; a.epi = epi; a.status = status;
+    a.tile_expert = tile_expert; a.expert_rows = N;
+    const size_t smem = (size_t)kStages * (kABytes + kBBytes) + (2 * kStages + 4) * 8 + 16 + 1024;
+    static bool opted_in = false;
+    if (!opted_in) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<EPI_GELU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tc_kernel<EPI_STORE_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "gemm_tc_grouped: %s", cudaGetErrorString(e));
+        opted_in = true;
+    }
+    const long long tiles = (long long)((N + BN - 1) / BN) * (M / BM);
+    const int grid = (int)(tiles < blm_sm_count() ? tiles : blm_sm_count());        // persistent: one block per SM
+    if (epi == EPI_GELU) gemm_tc_kernel<EPI_GELU><<<grid, kThreads, smem, stream>>>(a, xmap, wmap);
+    else gemm_tc_kernel<EPI_STORE_F32><<<grid, kThreads, smem, stream>>>(a, xmap, wmap);
+    return blm_check_launch("gemm_tc_grouped");
 }

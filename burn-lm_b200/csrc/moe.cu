@@ -1022,6 +1022,69 @@ BLM_API int blm_moe_experts(const void* h, int dtype, const float* weights, cons
 }
 
 // ---------------------------------------------------------------------------------------------
+// For the grouped product on tcgen05 (gemm_tc.cu): the pairs laid out expert by expert with every expert's share starting at
+// a multiple of `tile_rows` places.  place_of[pair] = its place; pair_of_place[place] = the pair, -1 for a place no pair
+// owns; tile_expert[tile] = the expert that owns the tile of places, -1 for none.  One block.
+// ---------------------------------------------------------------------------------------------
+__global__ void moe_group_padded_kernel(const int* __restrict__ ids, int n_pairs, int n_experts, int tile_rows, int max_tiles,
+                                        int* __restrict__ place_of, int* __restrict__ pair_of_place, int* __restrict__ tile_expert) {
+    extern __shared__ int counts[];      // [n_experts] counts, then [n_experts] cursors
+    int* cursor = counts + n_experts;
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) counts[e] = 0;
+    for (int t = threadIdx.x; t < max_tiles; t += blockDim.x) tile_expert[t] = -1;
+    for (int p = threadIdx.x; p < max_tiles * tile_rows; p += blockDim.x) pair_of_place[p] = -1;
+    __syncthreads();
+    for (int a = threadIdx.x; a < n_pairs; a += blockDim.x) atomicAdd(&counts[min(max(ids[a], 0), n_experts - 1)], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int tile = 0;
+        for (int e = 0; e < n_experts; ++e) {
+            cursor[e] = tile * tile_rows;
+            const int tiles = (counts[e] + tile_rows - 1) / tile_rows;
+            for (int t = 0; t < tiles && tile + t < max_tiles; ++t) tile_expert[tile + t] = e;
+            tile += tiles;
+        }
+    }
+    __syncthreads();
+    for (int a = threadIdx.x; a < n_pairs; a += blockDim.x) {
+        const int place = atomicAdd(&cursor[min(max(ids[a], 0), n_experts - 1)], 1);
+        place_of[a] = place;
+        pair_of_place[place] = a;
+    }
+}
+
+// xs[place] = h[token of the place's pair] (zeros for a place no pair owns), 16 bytes a thread and step
+__global__ void moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ h, const int* __restrict__ pair_of_place, __nv_bfloat16* __restrict__ xs,
+                                       int width, int top) {
+    const int place = blockIdx.x;
+    const int pair = pair_of_place[place];
+    const uint4* src = pair >= 0 ? reinterpret_cast<const uint4*>(h + (size_t)(pair / top) * width) : nullptr;
+    uint4* dst = reinterpret_cast<uint4*>(xs + (size_t)place * width);
+    for (int i = threadIdx.x; i < width / 8; i += blockDim.x) dst[i] = src ? src[i] : make_uint4(0, 0, 0, 0);
+}
+
+// How many tiles of `tile_rows` places the padded layout of n_pairs pairs over n_experts experts can take at most.
+BLM_API int blm_moe_padded_tiles(int n_pairs, int n_experts, int tile_rows) { return (n_pairs + tile_rows - 1) / tile_rows + n_experts; }
+
+BLM_API int blm_moe_group_padded(const int* ids, int n_pairs, int n_experts, int tile_rows, int* place_of, int* pair_of_place,
+                                 int* tile_expert, cudaStream_t stream) {
+    if (n_pairs == 0) return BLM_OK;
+    BLM_REQUIRE(n_pairs > 0 && n_experts > 0 && n_experts <= 4096 && tile_rows > 0, "moe_group_padded: bad sizes");
+    const int max_tiles = blm_moe_padded_tiles(n_pairs, n_experts, tile_rows);
+    moe_group_padded_kernel<<<1, 1024, 2 * (size_t)n_experts * sizeof(int), stream>>>(ids, n_pairs, n_experts, tile_rows, max_tiles, place_of,
+                                                                                      pair_of_place, tile_expert);
+    return blm_check_launch("moe_group_padded");
+}
+
+BLM_API int blm_moe_gather_rows(const void* h, const int* pair_of_place, void* xs, int n_places, int width, int top, cudaStream_t stream) {
+    if (n_places == 0) return BLM_OK;
+    BLM_REQUIRE(n_places > 0 && width > 0 && width % 8 == 0 && top > 0, "moe_gather_rows: bad sizes");
+    BLM_REQUIRE((((size_t)h | (size_t)xs) & 15) == 0, "moe_gather_rows: rows must be 16-byte aligned");
+    moe_gather_rows_kernel<<<n_places, 128, 0, stream>>>((const __nv_bfloat16*)h, pair_of_place, (__nv_bfloat16*)xs, width, top);
+    return blm_check_launch("moe_gather_rows");
+}
+
+// ---------------------------------------------------------------------------------------------
 // out[n] = sum_k (weight_k if the weight is on the output) y[place_of[n, k]] + extra[n]   (k in the order of the choice);
 // y may come in n_planes planes of [places][width] whose sum it is
 // ---------------------------------------------------------------------------------------------

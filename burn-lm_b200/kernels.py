@@ -9,6 +9,7 @@ functions raise.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_size_t, c_uint, c_ulonglong, c_void_p
 
 import torch
@@ -157,6 +158,9 @@ _protos = {
         "blm_moe_experts": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                             c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_void_p],
         "blm_moe_down_splits": [c_int, c_int, c_int, c_int, c_int, c_int],
+        "blm_moe_padded_tiles": [c_int, c_int, c_int],
+        "blm_moe_group_padded": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+        "blm_moe_gather_rows": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "blm_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     },
     "attention": {
@@ -185,6 +189,8 @@ _protos = {
         "blm_gemm_tc": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int, c_int,
                         c_void_p, c_void_p],
         "blm_gemm_tc_supported": [c_int, c_int, c_int],
+        "blm_gemm_tc_grouped": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p,
+                                c_int, c_void_p, c_void_p],
     },
     "gemm_sk": {
         "blm_gemm_sk": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_int, c_void_p, c_int,
@@ -518,6 +524,9 @@ def moe_experts(h, ids, weights, gate_up, down, extra=None, weight_on_input=True
         raise KernelError("moe_experts: extra must be [N, D] in the activations' dtype")
     dev = h.device
     pairs = n * top
+    if (unit == UNIT_GELU and not weight_on_input and h.dtype == torch.bfloat16 and pairs >= MOE_TC_PAIRS * e and d % 8 == 0 and ff % 8 == 0
+            and d >= 64 and ff >= 64 and e * max(d, ff) < (1 << 31)):
+        return _moe_experts_tc(h, ids, weights, gate_up, down, extra, out_dtype or h.dtype)
     offsets = torch.empty(e + 1, dtype=torch.int32, device=dev)
     order = torch.empty(pairs, dtype=torch.int32, device=dev)
     place_of = torch.empty(pairs, dtype=torch.int32, device=dev)
@@ -532,6 +541,43 @@ def moe_experts(h, ids, weights, gate_up, down, extra=None, weight_on_input=True
           _ptr(act), _ptr(y), n, d, ff, e, top, 1 if weight_on_input else 0, c_float(clamp_limit), c_float(clamp_alpha), int(unit), planes, stream, kernels=2)
     _call("moe", "blm_moe_combine", _ptr(y), _ptr(place_of), _ptr(weights), _ptr(extra), _ptr(out), _code(h.dtype), n, d, top,
           0 if weight_on_input else 1, _code(out.dtype), planes, stream)
+    return out
+
+
+# from this many (token, expert) pairs an expert on average, experts without a gate run on tcgen05 (BURN_LM_B200_MOE_TC_PAIRS=n
+# to measure another border)
+MOE_TC_PAIRS = int(os.environ.get("BURN_LM_B200_MOE_TC_PAIRS", "16"))
+MOE_TC_ROWS = 128       # rows of a tile of the tcgen05 product: an expert's share of the pairs starts at a multiple of it
+
+
+def _moe_experts_tc(h, ids, weights, up, down, extra, out_dtype):
+    """Experts without a gate for prompts, both products on the tcgen05 tensor cores: the pairs' token rows are gathered expert
+    by expert, every expert's share starting at a multiple of 128 places (a place no pair owns holds zeros), and one grouped
+    product runs over all experts at once (kernels of gemm_tc.cu: a table names the expert of every tile of places); the
+    first product's epilogue applies the exact GELU, the second leaves fp32 sums, and the sum over a token's experts weighs
+    them as ever.  Everything is sized by the token count alone, so a step can be captured."""
+    n, d = h.shape
+    e, ff, _ = up.shape
+    top = ids.shape[1]
+    pairs, dev, stream = n * top, h.device, _stream()
+    tiles = int(_lib("moe").blm_moe_padded_tiles(pairs, e, MOE_TC_ROWS))
+    places = tiles * MOE_TC_ROWS
+    place_of = torch.empty(pairs, dtype=torch.int32, device=dev)
+    pair_of_place = torch.empty(places, dtype=torch.int32, device=dev)
+    tile_expert = torch.empty(tiles, dtype=torch.int32, device=dev)
+    xs = torch.empty((places, d), dtype=torch.bfloat16, device=dev)
+    act = torch.empty((places, ff), dtype=torch.bfloat16, device=dev)
+    y = torch.empty((places, d), dtype=torch.float32, device=dev)
+    out = torch.empty((n, d), dtype=out_dtype, device=dev)
+    status = status_word(dev)
+    _call("moe", "blm_moe_group_padded", _ptr(ids), pairs, e, MOE_TC_ROWS, _ptr(place_of), _ptr(pair_of_place), _ptr(tile_expert), stream)
+    _call("moe", "blm_moe_gather_rows", _ptr(h), _ptr(pair_of_place), _ptr(xs), places, d, top, stream)
+    _call("gemm_tc", "blm_gemm_tc_grouped", _ptr(xs), c_longlong(d), _ptr(up), c_longlong(d), _ptr(act), c_longlong(ff), places, ff, d, e,
+          _ptr(tile_expert), 3, _ptr(status), stream)
+    _call("gemm_tc", "blm_gemm_tc_grouped", _ptr(act), c_longlong(ff), _ptr(down), c_longlong(ff), _ptr(y), c_longlong(d), places, d, ff, e,
+          _ptr(tile_expert), 4, _ptr(status), stream)
+    _call("moe", "blm_moe_combine", _ptr(y), _ptr(place_of), _ptr(weights), _ptr(extra), _ptr(out), _code(h.dtype), n, d, top,
+          1, _code(out.dtype), 1, stream)
     return out
 
 

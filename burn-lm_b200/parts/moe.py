@@ -129,6 +129,8 @@ class RoutedMoE(SigmoidMoE):
                 or spec.keep_groups * (spec.n_experts // spec.n_groups) < spec.top):
             raise ValueError(f"{spec.n_experts} experts in {spec.n_groups} groups of which {spec.keep_groups} are kept, for {spec.top} chosen")
         self.shared = None
+        if spec.unit == "gelu" and runtime.dtype == torch.bfloat16:
+            self.kernel_modules = ("elementwise", "moe", "gemm_tc")       # prompts run these experts' products on tcgen05
 
     UNITS = {"gated": K.UNIT_GATED, "gelu": K.UNIT_GELU, "gelu_tanh": K.UNIT_GELU_TANH}
 
