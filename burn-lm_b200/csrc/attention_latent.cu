@@ -22,15 +22,13 @@ BLM_API const char* blm_attention_latent_last_error() { return g_blm_error; }
 
 // lanes 2i and 2i + 1 of a rotated part (`halves`: lanes i and i + rot_dims / 2) turn by pos * freq[i]; lanes from rot_dims
 // on pass unchanged.  The angle, its sine and cosine are taken in fp64 and applied in fp32.
-__device__ __forceinline__ float rotated_lane(const float* src, int j, int rot_dims, int pos, const double* __restrict__ freq,
-                                              int halves) {
+// `turn`: (cosine, sine) of the token's angle for every pair, worked out once a token (the heads and the key part turn alike)
+__device__ __forceinline__ float rotated_lane(const float* src, int j, int rot_dims, const float2* __restrict__ turn, int halves) {
     if (j >= rot_dims) return src[j];
     const int half = rot_dims >> 1;
     const int i = halves ? (j < half ? j : j - half) : (j >> 1);
     const int ia = halves ? i : 2 * i, ib = halves ? i + half : 2 * i + 1;
-    double s, c;
-    sincos((double)pos * freq[i], &s, &c);
-    const float a = src[ia], b = src[ib], cf = (float)c, sf = (float)s;
+    const float a = src[ia], b = src[ib], cf = turn[i].x, sf = turn[i].y;
     return j == ib ? b * cf + a * sf : a * cf - b * sf;
 }
 
@@ -44,17 +42,24 @@ __global__ void latent_prepare_kernel(const float* __restrict__ qp, long long qp
                                       const int* __restrict__ block_table, int table_stride, int n_tokens, int H, int dk, int dr,
                                       int R, int page_size, int halves) {
     __shared__ float red[33];
+    extern __shared__ float2 turn[];            // [rot_dims / 2]
     const int n = blockIdx.x;
     const int seq = token_seq[n];
     const bool real = seq >= 0;                 // a row of no sequence leaves zeros and reaches no cache
     const int pos = real ? token_pos[n] : 0;
+    for (int i = threadIdx.x; i < rot_dims / 2; i += blockDim.x) {
+        double sn, cs;
+        sincos((double)pos * freq[i], &sn, &cs);
+        turn[i] = make_float2((float)cs, (float)sn);
+    }
+    __syncthreads();
     const float* qrow = qp + (size_t)n * qp_stride;
     if (q_full != nullptr) {                    // whole heads [unrotated | rotated | zeros up to hd_full], for the expanded keys
         for (int idx = threadIdx.x; idx < H * hd_full; idx += blockDim.x) {
             const int h = idx / hd_full, d = idx % hd_full;
             float v = 0.f;
             if (real && d < dk) v = qrow[(size_t)h * (dk + dr) + d];
-            else if (real && d < dk + dr) v = rotated_lane(qrow + (size_t)h * (dk + dr) + dk, d - dk, rot_dims, pos, freq, halves);
+            else if (real && d < dk + dr) v = rotated_lane(qrow + (size_t)h * (dk + dr) + dk, d - dk, rot_dims, turn, halves);
             q_full[((size_t)n * H + h) * hd_full + d] = from_f32<T>(v);
         }
     }
@@ -64,7 +69,7 @@ __global__ void latent_prepare_kernel(const float* __restrict__ qp, long long qp
     }
     for (int idx = threadIdx.x; q_full == nullptr && idx < H * dr; idx += blockDim.x) {
         const int h = idx / dr, j = idx % dr;
-        q_rot[((size_t)n * H + h) * dr + j] = real ? rotated_lane(qrow + (size_t)h * (dk + dr) + dk, j, rot_dims, pos, freq, halves) : 0.f;
+        q_rot[((size_t)n * H + h) * dr + j] = real ? rotated_lane(qrow + (size_t)h * (dk + dr) + dk, j, rot_dims, turn, halves) : 0.f;
     }
     if (!real) return;
     const float* row = dkv + (size_t)n * dkv_stride;
@@ -75,7 +80,7 @@ __global__ void latent_prepare_kernel(const float* __restrict__ qp, long long qp
     const int page = block_table[(size_t)slot_of_seq[seq] * table_stride + pos / page_size];
     T* dst = pool + ((size_t)page * page_size + pos % page_size) * (R + dr);
     for (int r = threadIdx.x; r < R; r += blockDim.x) dst[r] = from_f32<T>(row[r] * inv * c_weight[r]);
-    for (int j = threadIdx.x; j < dr; j += blockDim.x) dst[R + j] = from_f32<T>(rotated_lane(row + R, j, rot_dims, pos, freq, halves));
+    for (int j = threadIdx.x; j < dr; j += blockDim.x) dst[R + j] = from_f32<T>(rotated_lane(row + R, j, rot_dims, turn, halves));
 }
 
 BLM_API int blm_latent_prepare(const float* qp, long long qp_stride, const float* dkv, long long dkv_stride, const float* c_weight,
@@ -91,12 +96,12 @@ BLM_API int blm_latent_prepare(const float* qp, long long qp_stride, const float
     BLM_REQUIRE(q_full != nullptr ? hd_full >= dk + dr : (q_nope != nullptr && q_rot != nullptr),
                 "latent_prepare: whole heads of at least %d lanes, or the two parts", dk + dr);
     if (dtype == BLM_F32)
-        latent_prepare_kernel<float><<<n_tokens, 256, 0, stream>>>(qp, qp_stride, dkv, dkv_stride, c_weight, eps, freq, rot_dims,
+        latent_prepare_kernel<float><<<n_tokens, 256, (size_t)(rot_dims / 2 + 1) * sizeof(float2), stream>>>(qp, qp_stride, dkv, dkv_stride, c_weight, eps, freq, rot_dims,
                                                                    (float*)q_nope, q_rot, (float*)q_full, hd_full, (float*)pool, token_seq, token_pos,
                                                                    slot_of_seq, block_table, table_stride, n_tokens, H, dk, dr, R,
                                                                    page_size, halves);
     else if (dtype == BLM_BF16)
-        latent_prepare_kernel<__nv_bfloat16><<<n_tokens, 256, 0, stream>>>(qp, qp_stride, dkv, dkv_stride, c_weight, eps, freq, rot_dims,
+        latent_prepare_kernel<__nv_bfloat16><<<n_tokens, 256, (size_t)(rot_dims / 2 + 1) * sizeof(float2), stream>>>(qp, qp_stride, dkv, dkv_stride, c_weight, eps, freq, rot_dims,
                                                                            (__nv_bfloat16*)q_nope, q_rot, (__nv_bfloat16*)q_full, hd_full, (__nv_bfloat16*)pool,
                                                                            token_seq, token_pos, slot_of_seq, block_table,
                                                                            table_stride, n_tokens, H, dk, dr, R, page_size, halves);

@@ -147,15 +147,14 @@ __device__ __forceinline__ void stage_row<__nv_bfloat16>(float* dst, const __nv_
 // q goes to q_out, k and v to the token's place in the paged cache.  rms(x) = sqrt(mean(x^2) + eps).  A warp a head;
 // the angle, its sine and cosine in fp64, everything else fp32.
 // ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ float turned_lane(const float* src, const float* w, float inv, int j, int rot_dims, int halves, int pos,
-                                             const double* __restrict__ freq) {
+// `turn`: (cosine, sine) of the token's angle for every pair of turning lanes, worked out once a token (all heads turn alike)
+__device__ __forceinline__ float turned_lane(const float* src, const float* w, float inv, int j, int rot_dims, int halves,
+                                             const float2* __restrict__ turn) {
     if (j >= rot_dims) return src[j] * inv * (w ? w[j] : 1.f);
     const int half = rot_dims >> 1;
     const int i = halves ? (j < half ? j : j - half) : (j >> 1);
     const int ia = halves ? i : 2 * i, ib = halves ? i + half : 2 * i + 1;
-    double sn, cs;
-    sincos((double)pos * freq[i], &sn, &cs);
-    const float a = src[ia] * inv * (w ? w[ia] : 1.f), b = src[ib] * inv * (w ? w[ib] : 1.f), cf = (float)cs, sf = (float)sn;
+    const float a = src[ia] * inv * (w ? w[ia] : 1.f), b = src[ib] * inv * (w ? w[ib] : 1.f), cf = turn[i].x, sf = turn[i].y;
     return j == ib ? b * cf + a * sf : a * cf - b * sf;
 }
 
@@ -167,11 +166,18 @@ __global__ void head_norm_rope_append_kernel(const float* __restrict__ proj, lon
                                              const int* __restrict__ token_seq, const int* __restrict__ token_pos,
                                              const int* __restrict__ slot_of_seq, const int* __restrict__ block_table,
                                              int table_stride) {
+    extern __shared__ float2 turn[];                   // [rot_dims / 2]
     const int n = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
     const float* p = proj + (size_t)n * proj_stride;
     const int seq = token_seq[n];
     const bool real = seq >= 0;                        // a row of no sequence leaves zeros in q and reaches no cache
     const int pos = real ? token_pos[n] : 0;
+    for (int i = threadIdx.x; i < rot_dims / 2; i += blockDim.x) {
+        double sn, cs;
+        sincos((double)pos * freq[i], &sn, &cs);
+        turn[i] = make_float2((float)cs, (float)sn);
+    }
+    __syncthreads();
     T* kpage = nullptr;
     T* vpage = nullptr;
     int r = 0;
@@ -198,11 +204,11 @@ __global__ void head_norm_rope_append_kernel(const float* __restrict__ proj, lon
         }
         if (is_q) {
             T* dst = q_out + ((size_t)n * n_heads + head) * dk;
-            for (int d = lane; d < dk; d += 32) dst[d] = from_f32<T>(real ? turned_lane(src, w, inv, d, rot_dims, halves, pos, freq) : 0.f);
+            for (int d = lane; d < dk; d += 32) dst[d] = from_f32<T>(real ? turned_lane(src, w, inv, d, rot_dims, halves, turn) : 0.f);
         } else if (is_k) {
             if (!real) continue;
             T* dst = kpage + ((size_t)head * page_size + r) * dk;
-            for (int d = lane; d < dk; d += 32) dst[d] = from_f32<T>(turned_lane(src, w, inv, d, rot_dims, halves, pos, freq));
+            for (int d = lane; d < dk; d += 32) dst[d] = from_f32<T>(turned_lane(src, w, inv, d, rot_dims, halves, turn));
         } else {
             if (!real) continue;
             T* dst = vpage + ((size_t)head * page_size + r) * dv;
@@ -224,7 +230,7 @@ BLM_API int blm_head_norm_rope_append(const float* proj, long long proj_stride, 
     const int vectors = n_heads + 2 * n_kv;
     const int threads = vectors >= 8 ? 256 : 32 * vectors;
 #define BLM_HNRA(T)                                                                                                              \
-    head_norm_rope_append_kernel<T><<<n_tokens, threads, 0, stream>>>(proj, proj_stride, n_heads, n_kv, dk, dv, wq, wk, eps, value_norm, \
+    head_norm_rope_append_kernel<T><<<n_tokens, threads, (size_t)(rot_dims / 2 + 1) * sizeof(float2), stream>>>(proj, proj_stride, n_heads, n_kv, dk, dv, wq, wk, eps, value_norm, \
         freq, rot_dims, halves, (T*)q_out, (T*)pool, page_elems, page_size, token_seq, token_pos, slot_of_seq, block_table, table_stride)
     if (dtype == BLM_F32) BLM_HNRA(float);
     else if (dtype == BLM_BF16) BLM_HNRA(__nv_bfloat16);
